@@ -1,0 +1,176 @@
+/*
+ * dash_attn.h - C ABI of the B200 (sm_100a) attention library.
+ *
+ * Scaled dot-product attention with grouped key-value heads in its three forms: the packed /
+ * masked training forward with saved log-sum-exp, its written-out backward, and the decoding step
+ * against a key-value cache, as crates/dash-contract/src/attention.rs defines them.  These entry
+ * points are what a Rust `extern "C"` block would bind to sit behind dash-ops' backend-extension
+ * trait `AttentionBackend` (crates/dash-ops/src/attention.rs:289-352).
+ *
+ * Conventions (crates/dash-contract/src/lib.rs, crates/dash-ops/src/attention.rs:85-93):
+ *   - every pointer except the parameter structs is DEVICE memory owned by the caller; the library
+ *     allocates nothing and keeps nothing between calls; scratch comes in through `workspace`;
+ *   - work is enqueued on `stream` and the call returns without synchronising;
+ *   - layouts: q, o, do, dq [B,Tq,Hq,D]; k, v, dk, dv [B,Tk,Hkv,D]; lse [B,Tq,Hq] f32; decode
+ *     q / out [B,Hq,D], cache [B,S,Hkv,D], lengths [B];
+ *   - inputs may have any strides (given in ELEMENTS, order batch, time, head, dim); outputs are
+ *     written contiguous.  The tensor-core paths read an input in place when its last stride is 1,
+ *     its other strides are multiples of 8 elements (16-bit dtypes) and its base is 16-byte
+ *     aligned - the reference's own rule (crates/dash-ops/src/attention/cube.rs:428-461) - and any
+ *     other input is read, also in place, by the generic kernels: no input is ever copied;
+ *   - every function returning `int` gives DASH_ATTN_OK or an error code, and then
+ *     dash_attn_last_error() names the operation and the argument, with the reference's own
+ *     wording where it panics (crates/dash-ops/src/attention.rs:551-638).  Nothing is launched
+ *     when a call is refused.  There is no CPU fallback.
+ *   - re-entrant: no mutable global state beyond atomic counters and a thread-local error string.
+ */
+#ifndef DASH_ATTN_H
+#define DASH_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling the CUDA headers into the caller. */
+typedef struct CUstream_st *dash_attn_stream_t;
+
+/* crates/dash-contract/src/lib.rs:107-115 (DType): the dtype q, k and v share. */
+enum { DASH_ATTN_F32 = 0, DASH_ATTN_BF16 = 1, DASH_ATTN_F16 = 2 };
+
+/* crates/dash-contract/src/attention.rs:162-183 (AttentionMask). */
+enum { DASH_ATTN_MASK_NONE = 0, DASH_ATTN_MASK_KEY_PADDING = 1, DASH_ATTN_MASK_PACKED = 2 };
+
+enum {
+    DASH_ATTN_OK = 0,
+    DASH_ATTN_INVALID = 1,     /* the shapes do not fit together: where dash-ops panics */
+    DASH_ATTN_UNSUPPORTED = 2, /* a well-formed call this library does not take (conformance's Unsupported) */
+    DASH_ATTN_WORKSPACE = 3,   /* workspace missing, misaligned or smaller than *_workspace() says */
+    DASH_ATTN_CUDA = 4         /* a CUDA runtime or driver call failed; the message carries its text */
+};
+
+/* A window side with no bound (`usize::MAX` in crates/dash-contract/src/attention.rs:71-80). */
+#define DASH_ATTN_UNBOUNDED ((int64_t)-1)
+
+/*
+ * One training call: shapes, strides, mask and options as plain data.
+ * Mirrors the arguments of AttentionBackend::attention_forward / attention_backward
+ * (crates/dash-ops/src/attention.rs:307-337) with AttentionOptions
+ * (crates/dash-contract/src/attention.rs:88-103) flattened in.
+ */
+typedef struct dash_attn_params {
+    int32_t dtype;           /* DASH_ATTN_F32 / BF16 / F16 */
+    int32_t b, tq, tk, hq, hkv, d;
+    int32_t v_tk, v_hkv, v_d; /* value's own [Tk, Hkv, D]: "key and value must have one shape" */
+    int32_t k_b, k_d;        /* key's own batch size and head dimension, checked against q's */
+    int64_t q_stride[4], k_stride[4], v_stride[4]; /* elements: batch, time, head, dim */
+    int64_t o_stride[4], do_stride[4];             /* backward's inputs o and do (ignored by forward) */
+
+    int32_t mask_kind;       /* DASH_ATTN_MASK_* */
+    const void *key_padding; /* [B,Tk], non-zero = key left out */
+    int32_t key_padding_elem_bytes; /* 1 (bool / u8) or 4 (i32) */
+    int32_t key_padding_shape[2];   /* must equal [B, Tk] */
+    int64_t key_padding_stride[2];  /* elements */
+    const void *cu_seqlens_q; /* [S+1] */
+    const void *cu_seqlens_k; /* [S+1] */
+    int32_t cu_seqlens_q_len, cu_seqlens_k_len; /* S+1 each, one S */
+    int32_t index_elem_bytes; /* 4 (i32) or 8 (i64): the offsets' integer type */
+
+    int32_t causal;          /* 0 / 1 */
+    int32_t has_window;      /* 0: no window; 1: window_left / window_right apply */
+    int64_t window_left, window_right; /* DASH_ATTN_UNBOUNDED (any negative) = no bound */
+    int32_t has_scale;       /* 0: 1/sqrt(D), as (1.0 / (d as f64).sqrt()) as f32 */
+    float scale;
+    int32_t deterministic;   /* 1: the query gradient sums in a fixed order (default) */
+} dash_attn_params;
+
+/*
+ * One decoding step.  Mirrors AttentionBackend::attention_decode
+ * (crates/dash-ops/src/attention.rs:343-351) and check_decode_shapes (:617-638).  Of the options
+ * only the scale and the window's left side apply.
+ */
+typedef struct dash_attn_decode_params {
+    int32_t dtype;
+    int32_t b, s, hq, hkv, d;
+    int32_t k_b, k_d, v_b, v_s, v_hkv, v_d; /* the caches' own dims, checked against each other */
+    int64_t q_stride[3];                    /* elements: batch, head, dim */
+    int64_t k_stride[4], v_stride[4];       /* elements: batch, time, head, dim */
+    const void *lengths;       /* [B] or NULL: every sequence holds all S keys */
+    int32_t lengths_len;       /* must equal B when lengths != NULL */
+    int32_t lengths_elem_bytes; /* 4 or 8 */
+    int32_t has_window;
+    int64_t window_left;       /* DASH_ATTN_UNBOUNDED = no bound */
+    int32_t has_scale;
+    float scale;
+} dash_attn_decode_params;
+
+/* Bytes of device scratch each call needs (0 is possible).  256-byte aligned workspace. */
+size_t dash_attn_forward_workspace(const dash_attn_params *p);
+size_t dash_attn_backward_workspace(const dash_attn_params *p);
+size_t dash_attn_decode_workspace(const dash_attn_decode_params *p);
+
+/*
+ * Replaces AttentionBackend::attention_forward (crates/dash-ops/src/attention.rs:307-315; the
+ * reference's launch glue is crates/dash-ops/src/attention/cube.rs:562-684).
+ * o [B,Tq,Hq,D] in q's dtype and lse [B,Tq,Hq] f32, both contiguous.  A query that sees no key
+ * gives zeros and -inf.
+ */
+int dash_attn_forward(const dash_attn_params *p, const void *q, const void *k, const void *v,
+                      void *o, float *lse, void *workspace, size_t workspace_bytes,
+                      dash_attn_stream_t stream);
+
+/*
+ * Replaces AttentionBackend::attention_backward (crates/dash-ops/src/attention.rs:326-337; glue
+ * crates/dash-ops/src/attention/cube.rs:850-1120).  dq, dk, dv contiguous, each in its input's
+ * dtype.  lse is the forward's, contiguous [B,Tq,Hq] f32.
+ */
+int dash_attn_backward(const dash_attn_params *p, const void *q, const void *k, const void *v,
+                       const void *o, const float *lse, const void *dout, void *dq, void *dk,
+                       void *dv, void *workspace, size_t workspace_bytes,
+                       dash_attn_stream_t stream);
+
+/*
+ * Replaces AttentionBackend::attention_decode (crates/dash-ops/src/attention.rs:343-351; glue
+ * crates/dash-ops/src/attention/cube.rs:1126-1216).  out [B,Hq,D] contiguous in q's dtype; zeros
+ * for a sequence that holds no key.
+ */
+int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void *k_cache,
+                     const void *v_cache, void *out, void *workspace, size_t workspace_bytes,
+                     dash_attn_stream_t stream);
+
+/*
+ * Which kernels a call would run: 0 = the generic f32-FMA kernels (any dtype, any D <= 256, any
+ * strides), 1 = the tcgen05 tensor-core path, negative = refused (dash_attn_last_error() says
+ * why).  `backward` selects the pass.  The analogue of dash-ops' `kernels_take`
+ * (crates/dash-ops/src/attention.rs:814-821), for tests.
+ */
+int dash_attn_kernels_take(const dash_attn_params *p, const void *q, const void *k, const void *v,
+                           int backward);
+
+/* Thread-local text of the last refusal or failure on this thread ("" when none). */
+const char *dash_attn_last_error(void);
+
+/*
+ * Process-wide counters, the analogue of dash-ops' `probe` module
+ * (crates/dash-ops/src/attention.rs:158-221).
+ */
+enum {
+    DASH_ATTN_PROBE_KERNEL_LAUNCHES = 0, /* kernels this library launched */
+    DASH_ATTN_PROBE_BACKWARD_RUNS = 1,   /* calls of dash_attn_backward that launched */
+    DASH_ATTN_PROBE_INPUT_COPIES = 2,    /* always 0: every input is read in place */
+    DASH_ATTN_PROBE_ATOMIC_RUNS = 3,     /* backward passes that summed dq with atomics */
+    DASH_ATTN_PROBE_TENSOR_CORE_RUNS = 4, /* calls that took the tcgen05 path */
+    DASH_ATTN_PROBE_GENERIC_RUNS = 5,    /* calls that took the generic kernels */
+    DASH_ATTN_PROBE_COUNT = 6
+};
+uint64_t dash_attn_probe(int which);
+
+/* For tests: 0 = choose by the call (default), 1 = always the generic kernels. */
+void dash_attn_force_generic(int on);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DASH_ATTN_H */

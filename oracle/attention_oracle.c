@@ -157,3 +157,36 @@ static void build_hidden(const oracle_attn_params *p, int32_t bi, uint8_t *hidde
 #undef SUFFIX
 #undef EXP
 #undef LOG
+
+/* The seeded inputs of the reference's tests (crates/dash-conformance/src/attention.rs:433-452,
+ * crates/dash-ops/tests/attention_masks.rs:354-384): xorshift64 from seed * 0x9E3779B97F4A7C15 | 1,
+ * the top 24 bits as a uniform in [0, 1), mapped to about [-2, 2] and rounded to bf16. */
+static float round_to_bf16(float x) {
+    uint32_t bits;
+    memcpy(&bits, &x, 4);
+    bits = (bits + 0x7fffu + ((bits >> 16) & 1u)) & 0xffff0000u;
+    memcpy(&x, &bits, 4);
+    return x;
+}
+
+void oracle_seeded(float *out, int64_t n, uint64_t seed) {
+    uint64_t state = (seed * 0x9E3779B97F4A7C15ull) | 1ull;
+    for (int64_t i = 0; i < n; ++i) {
+        state ^= state << 13;
+        state ^= state >> 7;
+        state ^= state << 17;
+        float uniform = (float)(state >> 40) / (float)(1ull << 24);
+        out[i] = round_to_bf16((uniform - 0.5f) * 4.0f);
+    }
+}
+
+/* Deterministic booleans, true with probability p (attention_masks.rs:373-384). */
+void oracle_coins(uint8_t *out, int64_t n, float p, uint64_t seed) {
+    uint64_t state = (seed * 0x2545F4914F6CDD1Dull) | 1ull;
+    for (int64_t i = 0; i < n; ++i) {
+        state ^= state << 13;
+        state ^= state >> 7;
+        state ^= state << 17;
+        out[i] = ((float)(state >> 40) / (float)(1ull << 24)) < p;
+    }
+}

@@ -260,3 +260,19 @@ def numpy_decode(q, k, v, *, lengths=None, window_left=None, scale=None):
             e = np.exp(sc - sc.max())
             out[bi, h] = (e / e.sum()) @ v[bi, first:n, h // g]
     return out.astype(np.float32)
+
+
+def seeded(shape, seed: int) -> np.ndarray:
+    """Deterministic bf16-representable values in about [-2, 2], the reference tests' generator
+    (crates/dash-conformance/src/attention.rs:433-452)."""
+    out = np.empty(int(np.prod(shape)), np.float32)
+    lib().oracle_seeded(_ptr(out), ctypes.c_int64(out.size), ctypes.c_uint64(seed))
+    return out.reshape(shape)
+
+
+def coins(n: int, p: float, seed: int) -> np.ndarray:
+    """Deterministic booleans, true with probability ``p``
+    (crates/dash-ops/tests/attention_masks.rs:373-384)."""
+    out = np.empty(n, np.uint8)
+    lib().oracle_coins(_ptr(out), ctypes.c_int64(n), ctypes.c_float(p), ctypes.c_uint64(seed))
+    return out.astype(bool)

@@ -1,0 +1,235 @@
+"""The kernels against the CPU oracle at shapes of several tiles, as dash-ops holds its kernels to
+its reference (crates/dash-ops/tests/attention_masks.rs:740-1044, crates/dash-ops/tests/attention.rs)."""
+import numpy as np
+import pytest
+import torch
+
+import cases as K
+import records as R
+from adapter import Attention, AttentionDecode, B200Adapter
+from dashmag_b200 import _lib
+from dashmag_b200 import attention as A
+from dashmag_b200.contract import AttentionMask, AttentionOptions, DType
+from oracle import attention_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+# crates/dash-ops/tests/attention_masks.rs:294-305
+TILED = {
+    DType.BF16: [3.3e-3, 4.4e-7, 7.7e-3, 4.6e-3, 3.9e-3],
+    DType.F16: [4.1e-4, 4.4e-7, 7.3e-4, 6.8e-4, 4.9e-4],
+    # f32: 1e-5 of each result's largest value is the bound this build is held to; the log-sum-exp
+    # tighter, as in the reference's bounds.
+    DType.F32: [1e-5, 1e-6, 1e-5, 1e-5, 1e-5],
+}
+DECODE = {DType.BF16: 2.2e-3, DType.F16: 2.6e-4, DType.F32: 2e-6}
+
+
+@pytest.fixture(scope="module")
+def adapter():
+    return B200Adapter()
+
+
+def run_case(adapter, case, dtype, deterministic=True):
+    call = Attention(case.q, case.k, case.v, dtype, case.mask, case.options.with_deterministic(deterministic), case.grad)
+    return adapter.attention(call)
+
+
+def oracle_results(case):
+    kw = case.oracle_kwargs()
+    o, lse = oracle.forward(case.q, case.k, case.v, **kw)
+    dq, dk, dv = oracle.backward(case.q, case.k, case.v, o, lse, case.grad, **kw)
+    return [o, lse, dq, dk, dv]
+
+
+TILED_CASES = K.tiled_cases()
+
+
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16, DType.F16], ids=["f32", "bf16", "f16"])
+@pytest.mark.parametrize("case", TILED_CASES, ids=[c.name for c in TILED_CASES])
+def test_tiled_shapes_match_oracle(adapter, case, dtype):
+    got = run_case(adapter, case, dtype)
+    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), TILED[dtype])
+
+
+TC_CASES = K.tensor_core_cases()
+
+
+@pytest.mark.parametrize("deterministic", [True, False], ids=["det", "atomic"])
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F16, DType.F32], ids=["bf16", "f16", "f32"])
+@pytest.mark.parametrize("case", TC_CASES, ids=[c.name for c in TC_CASES])
+def test_tensor_core_shapes_match_oracle(adapter, case, dtype, deterministic):
+    got = run_case(adapter, case, dtype, deterministic)
+    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), TILED[dtype])
+
+
+@pytest.mark.parametrize("case", [TILED_CASES[0], TILED_CASES[10], TC_CASES[6]], ids=["none", "packed", "tc packed"])
+def test_same_bits_on_every_run_and_both_ways_of_summing(adapter, case):
+    """attention_masks.rs:818-899: deterministic runs repeat to the bit; with atomics o, dk and dv
+    are the deterministic run's bits and dq stays within |a|/128 + 1e-5 max."""
+    a = run_case(adapter, case, DType.BF16, True)
+    b = run_case(adapter, case, DType.BF16, True)
+    for x, y in zip([a.out, a.lse, *a.grads], [b.out, b.lse, *b.grads]):
+        assert np.array_equal(x, y, equal_nan=True)
+    c = run_case(adapter, case, DType.BF16, False)
+    assert np.array_equal(a.out, c.out) and np.array_equal(a.lse, c.lse)
+    assert np.array_equal(a.grads[1], c.grads[1]) and np.array_equal(a.grads[2], c.grads[2])
+    dq, dqa = a.grads[0], c.grads[0]
+    assert np.all(np.abs(dq - dqa) <= np.abs(dq) / 128 + 1e-5 * np.abs(dq).max())
+
+
+def test_head_dimension_outside_the_tensor_core_set(adapter):
+    """attention_masks.rs:902-931 runs D = 96 on the reference; here the generic kernels take it."""
+    case = K.seeded("D = 96", [2, 4, 2, 70, 90, 96], AttentionMask.none(), AttentionOptions.causal_(), 95)
+    for dtype in (DType.BF16, DType.F32):
+        got = run_case(adapter, case, dtype)
+        R.check(f"{dtype.name} D96", [got.out, got.lse, *got.grads], oracle_results(case), TILED[dtype])
+    odd = K.seeded("D = 51", [1, 3, 1, 37, 45, 51], AttentionMask.none(), AttentionOptions().with_window(9, 3), 96)
+    got = run_case(adapter, odd, DType.F32)
+    R.check("f32 D51", [got.out, got.lse, *got.grads], oracle_results(odd), TILED[DType.F32])
+
+
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16], ids=["f32", "bf16"])
+def test_two_causal_segments_compose_into_the_whole(adapter, dtype):
+    """attention_masks.rs:529-558, :936-970: segment 2's queries against both segments' keys
+    (bottom-right alignment) give the whole sequence's outputs; gradients add."""
+    t1, t = 150, 331
+    case = K.seeded("whole", [1, 4, 2, t, t, 128], AttentionMask.none(), AttentionOptions.causal_(), 200)
+    whole = run_case(adapter, case, dtype)
+    seg1 = adapter.attention(Attention(case.q[:, :t1], case.k[:, :t1], case.v[:, :t1], dtype, case.mask, case.options, case.grad[:, :t1]))
+    seg2 = adapter.attention(Attention(case.q[:, t1:], case.k, case.v, dtype, case.mask, case.options, case.grad[:, t1:]))
+    out = np.concatenate([seg1.out, seg2.out], 1)
+    lse = np.concatenate([seg1.lse, seg2.lse], 1)
+    dq = np.concatenate([seg1.grads[0], seg2.grads[0]], 1)
+    dk, dv = seg2.grads[1].copy(), seg2.grads[2].copy()
+    dk[:, :t1] += seg1.grads[1]
+    dv[:, :t1] += seg1.grads[2]
+    tol = {DType.F32: [2e-6, 5e-7, 2e-6, 2e-6, 2e-6], DType.BF16: [3.2e-3, 2.3e-7, 4.7e-3, 4.7e-3, 4.9e-3]}[dtype]
+    R.check(f"segments {dtype.name}", [out, lse, dq, dk, dv], [whole.out, whole.lse, *whole.grads], tol)
+
+
+def test_strided_inputs_are_read_in_place(adapter):
+    """crates/dash-ops/tests/attention.rs:498-525: head-major storage seen through a swap of the
+    time and head dimensions, and an input whose last stride is not 1, give the contiguous call's
+    results; nothing is copied."""
+    dev = adapter.device
+    case = K.seeded("strided", [2, 4, 2, 150, 190, 128], AttentionMask.none(), AttentionOptions.causal_(), 300)
+    want = oracle_results(case)
+    for dtype in (torch.bfloat16, torch.float32):
+        q, k, v, g = (torch.from_numpy(x).to(dev).to(dtype) for x in (case.q, case.k, case.v, case.grad))
+        # [B,H,T,D] storage viewed as [B,T,H,D]
+        qh, kh, vh, gh = (x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q, k, v, g))
+        assert not qh.is_contiguous()
+        before = _lib.probe("input_copies")
+        o, lse = A.attention_with_lse(qh, kh, vh, AttentionMask.none(), case.options)
+        dq, dk, dv = A.attention_backward(qh, kh, vh, o, lse, gh, AttentionMask.none(), case.options)
+        assert _lib.probe("input_copies") == before
+        tol = TILED[DType.BF16 if dtype == torch.bfloat16 else DType.F32]
+        R.check(f"head-major {dtype}", [x.float().cpu().numpy() for x in (o, lse, dq, dk, dv)], want, tol)
+        # last stride 2: every other element of a wider buffer
+        wide = lambda x: torch.stack([x, torch.zeros_like(x)], -1).flatten(-2)[..., ::2]
+        qs, ks, vs = wide(q), wide(k), wide(v)
+        assert qs.stride(-1) == 2
+        o2, lse2 = A.attention_with_lse(qs, ks, vs, AttentionMask.none(), case.options)
+        R.check(f"strided last dim {dtype}", [o2.float().cpu().numpy(), lse2.cpu().numpy()], want[:2], tol[:2])
+
+
+def decode_cases():
+    # [B, Hq, Hkv, S, D], lengths, window left
+    return [
+        ("full cache", [3, 8, 2, 300, 128], None, None),
+        ("mixed lengths incl. 0 and 1", [5, 4, 2, 257, 64], [257, 0, 1, 130, 64], None),
+        ("lengths, window 40", [4, 8, 2, 500, 128], [500, 17, 41, 333], 40),
+        ("window 0", [2, 4, 4, 90, 64], None, 0),
+        ("group of 8, D256", [2, 8, 1, 700, 256], [700, 123], None),
+        ("group of 3", [2, 6, 2, 200, 128], [150, 200], 64),
+        ("lengths past the cache and negative", [3, 4, 2, 100, 64], [1000, -5, 100], None),
+        ("odd head dimension", [2, 4, 2, 77, 40], [77, 30], 10),
+    ]
+
+
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16, DType.F16], ids=["f32", "bf16", "f16"])
+@pytest.mark.parametrize("name,dims,lengths,left", decode_cases(), ids=[c[0] for c in decode_cases()])
+def test_decode_matches_oracle(adapter, name, dims, lengths, left, dtype):
+    """attention_masks.rs:974-1044, attention.rs:528-628."""
+    b, hq, hkv, s, d = dims
+    q, k, v = oracle.seeded((b, hq, d), 500), oracle.seeded((b, s, hkv, d), 501), oracle.seeded((b, s, hkv, d), 502)
+    options = AttentionOptions() if left is None else AttentionOptions().with_window(left, 0)
+    got = adapter.attention_decode(AttentionDecode(q, k, v, dtype, lengths, options))
+    want = oracle.decode(q, k, v, lengths=lengths, window_left=left)
+    twin = oracle.numpy_decode(q, k, v, lengths=lengths, window_left=left)
+    assert np.max(np.abs(want - twin)) < 1e-6
+    abs_err, rel = R.errors(got, want)
+    print(f"decode {name} {dtype.name}: max abs {abs_err:.3e}, relative {rel:.3e} (tolerance {DECODE[dtype]:.1e})")
+    assert rel <= DECODE[dtype]
+    if lengths is not None:
+        for bi, n in enumerate(lengths):
+            if n <= 0:
+                assert np.all(got[bi] == 0.0), "a sequence holding no key gets zeros"
+
+
+def test_decode_large_cache_and_sliced_cache(adapter):
+    """attention.rs:542-547 ([8,8,2,1,6144,256]) and :600-628 (a slice of a longer cache read in place)."""
+    dev = adapter.device
+    b, hq, hkv, s, d = 8, 8, 2, 6144, 256
+    q, k, v = oracle.seeded((b, hq, d), 600), oracle.seeded((b, s, hkv, d), 601), oracle.seeded((b, s, hkv, d), 602)
+    lengths = [6144, 100, 3000, 1, 4097, 2048, 6143, 777]
+    got = adapter.attention_decode(AttentionDecode(q, k, v, DType.BF16, lengths, AttentionOptions()))
+    want = oracle.decode(q, k, v, lengths=lengths)
+    _, rel = R.errors(got, want)
+    assert rel <= DECODE[DType.BF16], rel
+    tq, tk, tv = (torch.from_numpy(x).to(dev).to(torch.bfloat16) for x in (q, k, v))
+    sliced = A.attention_decode(tq, tk[:, :1000], tv[:, :1000], None, AttentionOptions())
+    want = oracle.decode(q, k[:, :1000], v[:, :1000])
+    _, rel = R.errors(sliced.float().cpu().numpy(), want)
+    assert rel <= DECODE[DType.BF16], rel
+
+
+def test_degenerate_sizes(adapter):
+    """reference.rs:316-327, :386-395: no query, no key or no head dimension gives zeros and -inf."""
+    dev = adapter.device
+    q = torch.randn(2, 5, 4, 64, device=dev)
+    k = torch.randn(2, 0, 2, 64, device=dev)
+    o, lse = A.attention_with_lse(q, k, k.clone())
+    assert torch.all(o == 0) and torch.all(torch.isneginf(lse))
+    dq, dk, dv = A.attention_backward(q, k, k.clone(), o, lse, torch.ones_like(o))
+    assert torch.all(dq == 0) and dk.numel() == 0 and dv.numel() == 0
+    q0 = torch.randn(2, 0, 4, 64, device=dev)
+    k1 = torch.randn(2, 7, 2, 64, device=dev)
+    o, lse = A.attention_with_lse(q0, k1, k1.clone())
+    assert o.shape == (2, 0, 4, 64) and lse.shape == (2, 0, 4)
+    out = A.attention_decode(torch.randn(2, 4, 64, device=dev), k, k.clone())
+    assert torch.all(out == 0)
+
+
+def test_no_t_by_t_memory_and_launch_counts(adapter):
+    """attention.rs:677-739: at T = 8192 the forward and backward hold no T x T scores (largest
+    allocation under 256 MiB), copy no input, and launch 1 and at most 4 kernels."""
+    dev = adapter.device
+    b, hq, hkv, t, d = 1, 8, 2, 8192, 256
+    gen = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randn(b, t, hq, d, device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn(b, t, hkv, d, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(b, t, hkv, d, device=dev, generator=gen).to(torch.bfloat16)
+    g = torch.randn(b, t, hq, d, device=dev, generator=gen).to(torch.bfloat16)
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats(dev)
+    base = torch.cuda.memory_allocated(dev)
+    l0 = _lib.probe("kernel_launches")
+    o, lse = A.attention_with_lse(q, k, v, AttentionMask.none(), AttentionOptions.causal_())
+    l1 = _lib.probe("kernel_launches")
+    dq, dk, dv = A.attention_backward(q, k, v, o, lse, g, AttentionMask.none(), AttentionOptions.causal_())
+    l2 = _lib.probe("kernel_launches")
+    torch.cuda.synchronize()
+    assert l1 - l0 == 1 and 3 <= l2 - l1 <= 4
+    assert _lib.probe("input_copies") == 0
+    grown = torch.cuda.max_memory_allocated(dev) - base
+    assert grown < 256 * 2**20, f"forward + backward grew memory by {grown / 2**20:.0f} MiB"
+    # sampled rows against the oracle restricted to what they see (causal: keys 0..i)
+    rows = [0, 1, 127, 128, 4095, 8191]
+    qf, kf, vf = q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy()
+    for i in rows:
+        want, want_lse = oracle.numpy_forward(qf[:, i:i + 1], kf[:, :i + 1], vf[:, :i + 1])
+        got = o[:, i:i + 1].float().cpu().numpy()
+        assert np.max(np.abs(got - want)) <= 3.3e-3 * max(np.max(np.abs(want)), 1e-3) + 1e-2 * 0
+        assert abs(float(lse[0, i, 0]) - float(want_lse[0, 0, 0])) <= 1e-5 * max(1.0, abs(float(want_lse[0, 0, 0])))
