@@ -390,4 +390,65 @@ int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void
     return DASH_ATTN_OK;
 }
 
+int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, const void *k_cache,
+                            const void *v_cache, void *out, dash_attn_stream_t stream_) {
+    const char *op = "attention_decode (static scratch)";
+    g_error.clear();
+    int rc = check_decode(p);
+    if (rc != DASH_ATTN_OK) return rc;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const size_t eb = elem_bytes(p->dtype);
+    size_t ob = (size_t)p->b * p->hq * p->d * eb;
+    if (ob == 0) return DASH_ATTN_OK;
+    if (!out) return fail(DASH_ATTN_INVALID, "%s: the output is null", op);
+    if (p->s == 0) {
+        cudaError_t e = cudaMemsetAsync(out, 0, ob, stream);
+        return e == cudaSuccess ? DASH_ATTN_OK : cuda_fail(op, e);
+    }
+    if (!q || !k_cache || !v_cache) return fail(DASH_ATTN_INVALID, "%s: a tensor pointer is null", op);
+
+    // Fewer, longer splits until the partials fit the library's array.
+    const size_t capacity = dash::decode_static_capacity_floats();
+    const size_t per_split = (size_t)p->b * p->hq * ((size_t)p->d + 1) + 64;
+    if (per_split > capacity)
+        return fail(DASH_ATTN_UNSUPPORTED,
+                    "%s: B * Hq * (D + 1) = %zu floats of partial output exceed the library's %zu-float (16 MiB) "
+                    "scratch; use dash_attn_decode with a workspace", op, per_split - 64, capacity);
+    int chunk, splits;
+    decode_plan(p, &chunk, &splits);
+    while ((size_t)splits * per_split > capacity) {
+        chunk *= 2;
+        splits = (p->s + chunk - 1) / chunk;
+    }
+    float *scratch = nullptr;
+    cudaError_t e = dash::decode_static_scratch(&scratch);
+    if (e != cudaSuccess) return cuda_fail(op, e);
+
+    dash::DecodeArgs a{};
+    a.b = p->b; a.s = p->s; a.hq = p->hq; a.hkv = p->hkv; a.d = p->d;
+    a.scale = scale_for(p->has_scale, p->scale, p->d);
+    a.q = q;
+    a.q_sb = p->q_stride[0]; a.q_sh = p->q_stride[1]; a.q_sd = p->q_stride[2];
+    a.k = view(k_cache, p->k_stride);
+    a.v = view(v_cache, p->v_stride);
+    a.lengths = p->lengths;
+    a.len_bytes = p->lengths_elem_bytes;
+    int64_t none = (int64_t)p->s + 1;
+    a.left = (int)((p->has_window && p->window_left >= 0 && p->window_left < none) ? p->window_left : none);
+    a.chunk = chunk;
+    a.splits = splits;
+    a.part_o = scratch;
+    size_t o_floats = ((size_t)p->b * p->hq * splits * p->d + 63) & ~size_t(63);
+    a.part_lse = scratch + o_floats;
+    a.out = out;
+    bool vec = (p->d == 64 || p->d == 128 || p->d == 256) && vector_readable(q, p->q_stride, 3, eb) &&
+               vector_readable(k_cache, p->k_stride, 4, eb) && vector_readable(v_cache, p->v_stride, 4, eb);
+    int launches = 0;
+    e = dash::launch_decode(p->dtype, a, vec, stream, &launches);
+    g_probe[DASH_ATTN_PROBE_KERNEL_LAUNCHES] += launches;
+    g_probe[DASH_ATTN_PROBE_GENERIC_RUNS] += 1;
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return DASH_ATTN_OK;
+}
+
 }  // extern "C"

@@ -19,6 +19,8 @@
 //
 // Inputs the vector path cannot read (head dimension not 64 / 128 / 256, last stride not 1, rows
 // not 16-byte aligned) go through a slower scalar kernel with the same arithmetic.
+#include <mutex>
+
 #include "common.cuh"
 #include "launch.h"
 
@@ -304,6 +306,48 @@ cudaError_t launch_decode(int dtype, const DecodeArgs &a, bool vector_ok, cudaSt
         case 1: return decode_t<__nv_bfloat16>(a, vector_ok, stream, launches);
         default: return decode_t<__half>(a, vector_ok, stream, launches);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The decoding step with its scratch inside the library (dash_attn_decode_static)
+// ---------------------------------------------------------------------------------------------
+// Some callers hold nothing but the raw input and output buffers they were handed and have no way
+// to produce a workspace: an FFI shim under a tensor runtime whose memory pool owns all device
+// memory and is not reachable from C, or a serving loop that has promised not to allocate once it
+// is running.  For them the partial outputs of the split pass live in this file-scope array
+// instead of a caller-provided workspace.  Every GPU that loads the library reserves it until the
+// process exits, so it is kept modest: 4 Mi floats (16 MiB).
+//
+// In host code the array's name is only a stand-in; its device address is asked for once per
+// device (with that device current) and cached.  All calls share the array and it keeps whatever
+// the last call left in it: nothing in it needs to start at zero, because the merge pass reads
+// only the partials the split pass of the same call has just written - but two calls whose kernels
+// overlap on the GPU (different streams, or different host threads without ordering) would write
+// over each other's partials.
+constexpr size_t DECODE_STATIC_FLOATS = size_t(4) << 20;
+static __device__ __align__(256) float g_decode_static_scratch[DECODE_STATIC_FLOATS];
+
+size_t decode_static_capacity_floats() { return DECODE_STATIC_FLOATS; }
+
+// The device address of the static scratch on the current device; the first call on each device
+// resolves it (and should therefore come before any stream capture begins).
+cudaError_t decode_static_scratch(float **out) {
+    constexpr int MAX_DEVICES = 64;
+    static float *cache[MAX_DEVICES] = {};
+    static std::mutex lock;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!cache[dev]) {
+        float *ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_decode_static_scratch);
+        if (e != cudaSuccess) return e;
+        cache[dev] = ptr;
+    }
+    *out = cache[dev];
+    return cudaSuccess;
 }
 
 }  // namespace dash

@@ -141,6 +141,27 @@ int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void
                      dash_attn_stream_t stream);
 
 /*
+ * The decoding step for callers that cannot hand over a workspace.  It has no counterpart in the
+ * reference, whose launch glue always allocates its partial outputs from Burn's memory pool.
+ *
+ * Who needs it: code that is given raw device pointers and nothing else - an FFI shim sitting
+ * under a tensor runtime whose pool owns all device memory, a serving loop that must not allocate
+ * once it is running - and so can neither call cudaMalloc nor ask anyone for scratch.  The split
+ * pass's partial outputs live in a 16 MiB array inside the library (reserved on every GPU that
+ * loads it, until the process exits), and this call allocates nothing, on the device or through
+ * any library.  The result is dash_attn_decode's up to f32 rounding (the cache may be cut into
+ * fewer, longer splits so that the partials fit).
+ *
+ * Limits: B * Hq * (D + 1) floats per split must fit the array at least once, i.e.
+ * B * Hq * (D + 1) <= 4 Mi; larger calls return DASH_ATTN_UNSUPPORTED and say so.  All calls
+ * share the one array: calls whose kernels may overlap on the GPU (different streams, or threads
+ * without ordering between them) race on it - keep them on one stream.  The first call on each
+ * device looks up the array's device address; make that call before starting any stream capture.
+ */
+int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, const void *k_cache,
+                            const void *v_cache, void *out, dash_attn_stream_t stream);
+
+/*
  * Which kernels a call would run: 0 = the generic f32-FMA kernels (any dtype, any D <= 256, any
  * strides), 1 = the tcgen05 tensor-core path, negative = refused (dash_attn_last_error() says
  * why).  `backward` selects the pass.  The analogue of dash-ops' `kernels_take`
