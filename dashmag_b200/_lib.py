@@ -80,6 +80,7 @@ PROTOTYPES = {
     "dash_attn_decode": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
     "dash_attn_decode_static": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp]),
     "dash_attn_kernels_take": (ctypes.c_int, [ctypes.POINTER(Params), vp, vp, vp, ctypes.c_int]),
+    "dash_attn_device_status": (ctypes.c_int, [ctypes.c_int]),
     "dash_attn_last_error": (ctypes.c_char_p, []),
     "dash_attn_probe": (ctypes.c_uint64, [ctypes.c_int]),
     "dash_attn_force_generic": (None, [ctypes.c_int]),

@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "launch.h"
 #include "sm100.h"
+#include "sm100_kernels.h"
 
 namespace {
 
@@ -220,6 +221,14 @@ uint64_t dash_attn_probe(int which) {
 }
 
 void dash_attn_force_generic(int on) { g_force_generic.store(on ? 1 : 0); }
+
+int dash_attn_device_status(int clear) {
+    g_error.clear();
+    unsigned int status = 0;
+    cudaError_t e = dash::read_sm100_status(&status, clear != 0);
+    if (e != cudaSuccess) return -cuda_fail("device_status", e);
+    return (int)status;
+}
 
 int dash_attn_kernels_take(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
     g_error.clear();

@@ -1,0 +1,384 @@
+// The training forward on the 5th-generation tensor cores: bf16 / f16, head dimension 128.
+//
+// One block of 192 threads per (tile of 128 queries, query head):
+//   warp 0      one lane issues the TMA tile loads: the Q tile once, then K and V tiles of 128 keys
+//               into two-stage rings of 128-byte-swizzled shared memory;
+//   warp 1      owns tensor memory (512 columns: two S buffers and the O accumulator) and one lane
+//               issues the tcgen05 MMAs: S_j = Q K_j^T into the S buffer (j mod 2), O += P_j V_j;
+//   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S_j from tensor
+//               memory, mask what the row does not see, keep the online softmax in f32 with the
+//               scale folded into an exp2, write P_j rounded to the input dtype into shared memory
+//               in the layout of an MMA A operand, and at the end normalise O and store it with
+//               the row's log-sum-exp.
+// The S buffers and the P buffers are double, so QK^T of the next key tile runs under the softmax
+// of the current one, and P V of the current one under the softmax of the next.
+//
+// The running maximum is "lazy": the accumulator is rescaled only when a row's maximum grows by
+// more than 2^8, otherwise the stale maximum stays the reference of the exponentials (their sum and
+// the accumulator carry the same factor, which the final division removes).  The log-sum-exp is
+// formed in f32 from that reference and the f32 sum.
+//
+// Masks: every query's visible keys are one interval (common.cuh); a block sweeps the key tiles of
+// the union of its rows' intervals, elementwise masking runs only on tiles that cut some row's
+// interval or carry key padding, and out-of-range rows and keys are zero-filled by the TMA loads.
+// Every wait on an mbarrier is bounded; a wait that runs out raises a status flag the host can
+// read and the block leaves through the common teardown, so a fault in the pipeline cannot hang.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.h"
+#include "sm100_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace dash {
+
+using namespace ptx;
+
+__device__ unsigned int g_sm100_status = 0;  // sticky: non-zero once any bounded wait has run out
+
+namespace {
+
+constexpr int BM = 128;          // queries per block
+constexpr int BN = 128;          // keys per tile
+constexpr int HD = 128;          // head dimension
+constexpr int TILE_BYTES = BM * HD * 2;  // 32 KiB: any of the Q, K, V, P tiles
+constexpr int HALF_BYTES = TILE_BYTES / 2;  // one 64-column half: 128 rows of 128 bytes
+constexpr int THREADS = 192;
+constexpr float RESCALE_LOG2 = 8.0f;
+
+struct Barriers {
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_ready;
+};
+
+struct Shared {
+    Barriers bar;
+    uint32_t tmem_base;
+    int red_lo[4], red_hi[4];
+    unsigned int abort;
+};
+
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + 7 * TILE_BYTES /*Q, 2 K, 2 V, 2 P*/ + 1024 /*Shared*/;
+
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+    static constexpr int FMT = 1;
+    static __device__ __forceinline__ uint32_t two(float a, float b) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+template <> struct Pack<__half> {
+    static constexpr int FMT = 0;
+    static __device__ __forceinline__ uint32_t two(float a, float b) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+
+}  // namespace
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const Sm100FwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *q_s = smem;
+    uint8_t *k_s = q_s + TILE_BYTES;
+    uint8_t *v_s = k_s + 2 * TILE_BYTES;
+    uint8_t *p_s = v_s + 2 * TILE_BYTES;
+    Shared &sh = *reinterpret_cast<Shared *>(p_s + 2 * TILE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x;
+    const int qt = gridDim.y - 1 - blockIdx.y;  // later (longer, under causality) tiles first
+    const int b = blockIdx.z;
+    const int hk = h / (a.hq / a.hkv);
+    const int m0 = qt * BM;
+
+    const uint32_t q_full = smem_u32(&sh.bar.q_full), o_ready = smem_u32(&sh.bar.o_ready);
+    auto BAR = [&](uint64_t (&arr)[2], int i) { return smem_u32(&arr[i]); };
+
+    if (threadIdx.x == 0) {
+        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_status);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(sh.bar.k_full, i), 1);
+            mbar_init(BAR(sh.bar.k_empty, i), 1);
+            mbar_init(BAR(sh.bar.v_full, i), 1);
+            mbar_init(BAR(sh.bar.v_empty, i), 1);
+            mbar_init(BAR(sh.bar.s_full, i), 1);
+            mbar_init(BAR(sh.bar.s_empty, i), 128);
+            mbar_init(BAR(sh.bar.p_full, i), 128);
+            mbar_init(BAR(sh.bar.p_empty, i), 1);
+        }
+        mbar_init(o_ready, 1);
+        fence_mbar_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&sh.tmem_base), 512);
+        tmem_relinquish();
+    }
+
+    // Each softmax thread owns one query row; the block sweeps the union of its rows' intervals.
+    const int sw = warp - 2;                       // 0..3 for softmax warps
+    const int lane_base = 32 * (warp & 3);         // the TMEM lanes this warp may touch
+    const int r = lane_base + lane;                // row of the tile (softmax threads)
+    int lo = a.tk, hi = 0;
+    if (warp >= 2) {
+        row_bounds(a.mask, m0 + r, a.tq, a.tk, lo, hi);
+        int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
+        if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh.tmem_base;
+    int kmin = a.tk, kmax = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { kmin = min(kmin, sh.red_lo[i]); kmax = max(kmax, sh.red_hi[i]); }
+    // Once a bounded wait has run out anywhere, later blocks do nothing: the call has failed and
+    // the host will say so; there is no point in timing out thousands of times.
+    const bool aborted = sh.abort != 0;
+    const int n_tiles = (!aborted && kmax > kmin) ? (kmax - kmin + BN - 1) / BN : 0;
+    bool failed = aborted;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && n_tiles > 0) {
+            mbar_expect_tx(q_full, TILE_BYTES);
+            tma_load_4d(smem_u32(q_s), &tm_q, q_full, 0, h, m0, b);
+            tma_load_4d(smem_u32(q_s + HALF_BYTES), &tm_q, q_full, 64, h, m0, b);
+            for (int j = 0; j < n_tiles && !failed; ++j) {
+                const int st = j & 1, ph = (j >> 1) & 1, k0 = kmin + j * BN;
+                if (!mbar_wait(BAR(sh.bar.k_empty, st), ph ^ 1)) { failed = true; break; }
+                uint32_t full = BAR(sh.bar.k_full, st), dst = smem_u32(k_s + st * TILE_BYTES);
+                mbar_expect_tx(full, TILE_BYTES);
+                tma_load_4d(dst, &tm_k, full, 0, hk, k0, b);
+                tma_load_4d(dst + HALF_BYTES, &tm_k, full, 64, hk, k0, b);
+                if (!mbar_wait(BAR(sh.bar.v_empty, st), ph ^ 1)) { failed = true; break; }
+                full = BAR(sh.bar.v_full, st);
+                dst = smem_u32(v_s + st * TILE_BYTES);
+                mbar_expect_tx(full, TILE_BYTES);
+                tma_load_4d(dst, &tm_v, full, 0, hk, k0, b);
+                tma_load_4d(dst + HALF_BYTES, &tm_v, full, 64, hk, k0, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, Pack<T>::FMT, 0, 0);   // A = Q, B = K, both K-major
+            constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // A = P K-major, B = V MN-major
+            const uint32_t q_addr = smem_u32(q_s);
+            auto issue_pv = [&](int i) -> bool {
+                const int st = i & 1, ph = (i >> 1) & 1;
+                if (!mbar_wait(BAR(sh.bar.v_full, st), ph)) return false;
+                if (!mbar_wait(BAR(sh.bar.p_full, st), ph)) return false;
+                tc_fence_after_sync();
+                const uint32_t p_addr = smem_u32(p_s + st * TILE_BYTES), v_addr = smem_u32(v_s + st * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    // A: 16 keys = 32 bytes along the swizzled row, the second 64 keys in the second half.
+                    uint64_t ad = smem_desc_sw128(p_addr + (ks >> 2) * HALF_BYTES + (ks & 3) * 32, 16, 1024);
+                    // B: V rows are keys (K of this product), 128 bytes of head dimension per row and
+                    // half: 64-column atoms HALF_BYTES apart (leading), 8-key groups 1024 bytes apart.
+                    uint64_t bd = smem_desc_sw128(v_addr + ks * 2048, HALF_BYTES, 1024);
+                    umma_f16(tmem + 256, ad, bd, IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(BAR(sh.bar.v_empty, st));
+                umma_commit(BAR(sh.bar.p_empty, st));
+                umma_commit(o_ready);
+                return true;
+            };
+            if (!mbar_wait(q_full, 0)) failed = true;
+            for (int j = 0; j < n_tiles && !failed; ++j) {
+                const int st = j & 1, ph = (j >> 1) & 1;
+                if (!mbar_wait(BAR(sh.bar.k_full, st), ph) || !mbar_wait(BAR(sh.bar.s_empty, st), ph ^ 1)) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t k_addr = smem_u32(k_s + st * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+                    umma_f16(tmem + st * BN, smem_desc_sw128(q_addr + off, 16, 1024),
+                             smem_desc_sw128(k_addr + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(BAR(sh.bar.k_empty, st));
+                umma_commit(BAR(sh.bar.s_full, st));
+                if (j > 0 && !issue_pv(j - 1)) { failed = true; break; }
+            }
+            if (!failed && !issue_pv(n_tiles - 1)) failed = true;
+        }
+    } else {
+        // ---------------- softmax, one row per thread ----------------
+        const int row = m0 + r;
+        const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
+        const bool padded = a.mask.kind == 1;
+        float m_ref = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_tiles && !failed; ++j) {
+            const int st = j & 1, ph = (j >> 1) & 1, k0 = kmin + j * BN;
+            uint32_t pb[4] = {0, 0, 0, 0};
+            if (padded) {
+                // The tile's 128 padding flags as four words; every warp gathers its own copy, so
+                // that no softmax warp ever waits on another.
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = k0 + i * 32 + lane;
+                    pb[i] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
+                }
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full, st), ph))) { failed = true; break; }
+            tc_fence_after_sync();
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + st * BN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            mbar_arrive(BAR(sh.bar.s_empty, st));
+
+            const bool clear = !padded && k0 >= lo && k0 + BN <= hi;  // the row sees the whole tile
+            if (!__all_sync(0xffffffffu, clear)) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int key = k0 + c;
+                    const bool vis = key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u);
+                    s[c] = vis ? s[c] : -INFINITY;
+                }
+            }
+            float mx = s[0];
+#pragma unroll
+            for (int c = 1; c < BN; ++c) mx = fmaxf(mx, s[c]);
+            // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8.
+            float factor = 1.f;
+            bool rescale = false;
+            if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated yet for this row (or exact zeros)
+            } else if ((mx - m_ref) * a.scale_log2 > RESCALE_LOG2) {
+                factor = ex2((m_ref - mx) * a.scale_log2);
+                l *= factor;
+                m_ref = mx;
+                rescale = true;
+            }
+            const float neg = m_ref == -INFINITY ? 0.f : -m_ref * a.scale_log2;
+
+            // The P buffer is free once P V of tile j - 2 has completed.
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_empty, st), ph ^ 1))) { failed = true; break; }
+            uint8_t *p_row = p_s + st * TILE_BYTES + r * 128;
+            float sum = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < BN / 8; ++cc) {
+                float p[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    p[e] = ex2(fmaf(s[cc * 8 + e], a.scale_log2, neg));
+                    sum += p[e];
+                }
+                uint4 v = make_uint4(Pack<T>::two(p[0], p[1]), Pack<T>::two(p[2], p[3]), Pack<T>::two(p[4], p[5]),
+                                     Pack<T>::two(p[6], p[7]));
+                // 16-byte chunk (cc mod 8) of the row's 128 bytes in half (cc / 8), XOR-swizzled by the row.
+                *reinterpret_cast<uint4 *>(p_row + (cc >> 3) * HALF_BYTES + (((cc & 7) ^ (r & 7)) << 4)) = v;
+            }
+            l += sum;
+
+            // O holds tiles 0..j-1 once P V of tile j - 1 has completed; rescale it before P V of tile j.
+            if (j > 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1))) { failed = true; break; }
+                if (__any_sync(0xffffffffu, rescale)) {
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(t_lane + 256 + c * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                        tmem_st32(t_lane + 256 + c * 32, o);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(BAR(sh.bar.p_full, st));
+        }
+
+        // ---------------- epilogue ----------------
+        T *out = static_cast<T *>(a.out);
+        const int64_t base = ((int64_t)b * a.tq + row) * a.hq + h;
+        if (n_tiles == 0 || failed) {
+            if (row < a.tq && !failed) {
+                uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
+                a.lse[base] = -INFINITY;
+            }
+        } else if (__all_sync(0xffffffffu, mbar_wait(o_ready, (n_tiles - 1) & 1))) {
+            tc_fence_after_sync();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_lane + 256 + c * 32, o);
+                tmem_ld_wait();
+                if (row < a.tq) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
+                        v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
+                        v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
+                        v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
+                        reinterpret_cast<uint4 *>(out + base * HD)[c * 4 + e] = v;
+                    }
+                }
+            }
+            if (row < a.tq) a.lse[base] = l > 0.f ? m_ref * a.scale + logf(l) : -INFINITY;
+            tc_fence_before_sync();
+        } else {
+            failed = true;
+        }
+    }
+
+    if (failed && !aborted) atomicOr(&g_sm100_status, 1u);
+    // Teardown: every thread gets here (all waits are bounded); the allocating warp frees TMEM.
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
+                             const Sm100FwdArgs &a, cudaStream_t stream) {
+    dim3 grid(a.hq, (a.tq + BM - 1) / BM, a.b);
+    cudaError_t e;
+    if (dtype == DASH_ATTN_BF16) {
+        e = cudaFuncSetAttribute(fwd_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        fwd_sm100_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
+    } else {
+        e = cudaFuncSetAttribute(fwd_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        fwd_sm100_kernel<__half><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t read_sm100_status(unsigned int *status, bool clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_sm100_status, sizeof(unsigned int));
+    if (e != cudaSuccess) return e;
+    if (clear && *status) {
+        unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(unsigned int));
+    }
+    return e;
+}
+
+}  // namespace dash

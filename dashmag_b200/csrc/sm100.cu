@@ -1,18 +1,132 @@
+// Host side of the tcgen05 path: which calls it takes, the TMA tensor maps over the caller's
+// tensors, and the launches.
 #include "sm100.h"
 
+#include <cuda.h>
+
+#include <cmath>
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
+#include "sm100_kernels.h"
 
 namespace dash {
-bool sm100_takes(const dash_attn_params *, const void *, const void *, const void *, int) { return false; }
+
+namespace {
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library carries no
+// link-time dependency on libcuda (it must load on machines without a driver).
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    });
+    return fn;
+}
+
+// Whether the current device is a compute-capability-10 part; -1 unknown, cached per device.
+bool device_is_sm100() {
+    static int cache[64];
+    static std::once_flag once;
+    std::call_once(once, [] { for (int &c : cache) c = -1; });
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return false; }
+    if (cache[dev] < 0) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        cache[dev] = major == 10 ? 1 : 0;
+    }
+    return cache[dev] == 1;
+}
+
+// The reference's in-place rule (crates/dash-ops/src/attention/cube.rs:428-461), which is also what
+// a TMA tensor map needs: last stride 1, the others multiples of 16 bytes, base 16-byte aligned.
+bool tma_readable(const void *ptr, const int64_t *stride) {
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0 || stride[3] != 1) return false;
+    for (int i = 0; i < 3; ++i)
+        if (stride[i] % 8 != 0 || stride[i] < 0) return false;
+    return true;
+}
+
+// A [B, T, H, 128] tensor of 16-bit elements as a 4-D map (d, h, t, b) with boxes of 64 x 1 x 128 x 1
+// and the 128-byte swizzle: each load brings 128 rows of 128 bytes of one head.
+bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride) {
+    EncodeTiled fn = encoder();
+    if (!fn) return false;
+    auto bytes = [](int64_t elems) { return static_cast<cuuint64_t>(elems) * 2; };
+    cuuint64_t dims[4] = {128, (cuuint64_t)h, (cuuint64_t)t, (cuuint64_t)b};
+    // A dimension of extent 1 never moves: give it any legal stride.
+    cuuint64_t strides[3] = {h > 1 ? bytes(stride[2]) : 256, t > 1 ? bytes(stride[1]) : 256, b > 1 ? bytes(stride[0]) : 256};
+    for (cuuint64_t s : strides)
+        if (s == 0 || s % 16 != 0 || s >= (1ull << 40)) return false;
+    cuuint32_t box[4] = {64, 1, 128, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    CUtensorMapDataType dt = dtype == DASH_ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+float resolved_scale(const dash_attn_params *p) {
+    return p->has_scale ? p->scale : (float)(1.0 / std::sqrt((double)p->d));
+}
+
+}  // namespace
+
+bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
+    if (backward) return false;  // the backward runs the generic kernels
+    if (p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16) return false;
+    if (p->d != 128) return false;
+    const float scale = resolved_scale(p);
+    if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
+    if (!q || !k || !v) return false;
+    if (!tma_readable(q, p->q_stride) || !tma_readable(k, p->k_stride) || !tma_readable(v, p->v_stride)) return false;
+    if (p->hq > 65535 || p->b > 65535) return false;
+    if (!device_is_sm100() || !encoder()) return false;
+    return true;
+}
+
 size_t sm100_forward_workspace(const dash_attn_params *) { return 0; }
 size_t sm100_backward_workspace(const dash_attn_params *) { return 0; }
-cudaError_t sm100_forward(const dash_attn_params *, const TrainArgs &, void *, cudaStream_t, int *, std::string &err) {
-    err = "attention: the tensor-core path is not built";
-    return cudaSuccess;
+
+cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *, cudaStream_t stream, int *launches,
+                          std::string &err) {
+    CUtensorMap tq, tk, tv;
+    if (!encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride) ||
+        !encode(&tk, p->dtype, a.k.ptr, p->b, p->tk, p->hkv, p->k_stride) ||
+        !encode(&tv, p->dtype, a.v.ptr, p->b, p->tk, p->hkv, p->v_stride)) {
+        err = "attention: the driver refused a TMA tensor map over the inputs";
+        return cudaSuccess;
+    }
+    Sm100FwdArgs f{};
+    f.b = p->b; f.tq = p->tq; f.tk = p->tk; f.hq = p->hq; f.hkv = p->hkv;
+    f.scale = a.scale;
+    f.scale_log2 = a.scale * 1.4426950408889634f;
+    f.out = a.out;
+    f.lse = a.lse;
+    f.mask = a.mask;
+    cudaError_t e = launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream);
+    *launches += 1;
+    return e;
 }
+
 cudaError_t sm100_backward(const dash_attn_params *, const TrainArgs &, void *, cudaStream_t, int *, bool *,
                            std::string &err) {
-    err = "attention_backward: the tensor-core path is not built";
+    err = "attention_backward: the tensor-core path has no backward";
     return cudaSuccess;
 }
+
 }  // namespace dash

@@ -170,6 +170,16 @@ int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, con
 int dash_attn_kernels_take(const dash_attn_params *p, const void *q, const void *k, const void *v,
                            int backward);
 
+/*
+ * Every wait inside the tensor-core kernels is bounded; one that runs out raises a sticky word on
+ * the device instead of hanging, and later blocks and launches of those kernels then do nothing.
+ * This reads that word (0 = healthy) and, with `clear` non-zero, resets it.  It synchronises with
+ * the device, so it is for tests and for error paths, not for the hot loop.  Returns a negative
+ * DASH_ATTN_* code if the word cannot be read.  The reference has no counterpart: its kernels
+ * have no device-side waits.
+ */
+int dash_attn_device_status(int clear);
+
 /* Thread-local text of the last refusal or failure on this thread ("" when none). */
 const char *dash_attn_last_error(void);
 
