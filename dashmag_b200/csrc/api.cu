@@ -337,7 +337,7 @@ int dash_attn_backward(const dash_attn_params *p, const void *q, const void *k, 
     a.dq = dq; a.dk = dk; a.dv = dv;
     void *extra = static_cast<char *>(workspace) + align256(sizeof(float) * (size_t)p->b * p->tq * p->hq);
     cudaError_t e;
-    if (train_path(p, q, k, v, 1) == 1) {
+    if (train_path(p, q, k, v, 1) == 1 && reinterpret_cast<uintptr_t>(dout) % 16 == 0) {
         bool atomic = false;
         e = dash::sm100_backward(p, a, extra, stream, &launches, &atomic, g_error);
         if (e == cudaSuccess && !g_error.empty()) return DASH_ATTN_CUDA;

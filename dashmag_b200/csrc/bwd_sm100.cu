@@ -1,0 +1,622 @@
+// The written-out backward on the 5th-generation tensor cores: bf16 / f16, head dimension 128.
+//
+// Two kernels, neither with atomics, so every gradient is summed in a fixed order and the bits
+// repeat from run to run (the contract's default, crates/dash-contract/src/attention.rs:96-102):
+//
+//   dkdv   one block per (128 keys, key-value head).  K_j and V_j stay in shared memory; the block
+//          sweeps the query heads of the group and, in steps of 64, the queries that see the key
+//          block.  Per step:  S^T = K_j Q^T and dP^T = V_j dO^T on the tensor cores (TMEM lane =
+//          key), P^T = exp2(S^T sl - lse) and dS^T = P^T (dP^T - delta) elementwise, rounded to the
+//          input dtype into shared memory, then dV += P^T dO and dK += dS^T Q, accumulated in TMEM
+//          over the whole sweep.
+//   dq     one block per (128 queries, query head).  Q_i and dO_i stay in shared memory; the block
+//          sweeps, in steps of 64, the keys its queries see.  Per step: S = Q_i K^T, dP = dO_i V^T,
+//          dS = P (dP - delta), then dQ += dS K.
+//
+// Both recompute the scores tile by tile from the saved log-sum-exp (no T x T anywhere): seven
+// 128-deep products per pair of tiles.  The streamed tiles serve twice from one copy in shared
+// memory - K-major for the score products and MN-major for the gradient products - through two
+// descriptors over the same 128-byte-swizzled bytes.  Warp roles as in the forward: warp 0 issues
+// TMA loads (and, in dkdv, gathers the step's per-query log-sum-exp, delta and key interval),
+// warp 1 issues the MMAs and owns TMEM, warps 2..5 do the elementwise work, one TMEM lane each.
+// The score buffers and the P / dS buffers are double, so the products of one step run under the
+// elementwise work of its neighbours.  Every mbarrier wait is bounded (sm100_ptx.cuh).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.h"
+#include "sm100_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace dash {
+
+using namespace ptx;
+
+extern __device__ unsigned int g_sm100_status;
+
+namespace {
+
+constexpr int BIG = 128;                   // rows of the resident tile (and TMEM lanes)
+constexpr int STEP = 64;                   // rows of a streamed tile
+constexpr int HD = 128;
+constexpr int BIG_BYTES = BIG * HD * 2;    // 32 KiB
+constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes
+constexpr int STEP_BYTES = STEP * HD * 2;  // 16 KiB
+constexpr int STEP_HALF = STEP_BYTES / 2;  // 64 rows of 128 bytes
+constexpr int PS_BYTES = BIG * STEP * 2;   // 16 KiB: a P^T / dS^T / dS tile, 128 rows of 128 bytes
+constexpr int THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+    static constexpr int FMT = 1;
+    static __device__ __forceinline__ uint32_t two(float a, float b) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+template <> struct Pack<__half> {
+    static constexpr int FMT = 0;
+    static __device__ __forceinline__ uint32_t two(float a, float b) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+
+// Row `r` of a [128 x 64] 16-bit tile in the layout of a K-major MMA operand: 128 bytes per row,
+// 16-byte chunks XOR-swizzled by the row.
+template <typename T>
+__device__ __forceinline__ void store_row64(uint8_t *tile, int r, const float (&x)[STEP]) {
+    uint8_t *row = tile + r * 128;
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc) {
+        uint4 v = make_uint4(Pack<T>::two(x[cc * 8 + 0], x[cc * 8 + 1]), Pack<T>::two(x[cc * 8 + 2], x[cc * 8 + 3]),
+                             Pack<T>::two(x[cc * 8 + 4], x[cc * 8 + 5]), Pack<T>::two(x[cc * 8 + 6], x[cc * 8 + 7]));
+        *reinterpret_cast<uint4 *>(row + ((cc ^ (r & 7)) << 4)) = v;
+    }
+}
+
+// 128 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as one
+// contiguous row of 128 elements.
+template <typename T>
+__device__ __forceinline__ void store_acc_row(uint32_t taddr, T *dst, float scale, bool write) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(taddr + c * 32, o);
+        tmem_ld_wait();
+        if (write) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                uint4 v;
+                v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * scale, __uint_as_float(o[8 * e + 1]) * scale);
+                v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * scale, __uint_as_float(o[8 * e + 3]) * scale);
+                v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * scale, __uint_as_float(o[8 * e + 5]) * scale);
+                v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * scale, __uint_as_float(o[8 * e + 7]) * scale);
+                reinterpret_cast<uint4 *>(dst)[c * 4 + e] = v;
+            }
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_zero_row(T *dst) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+}
+
+// The queries [first, end) that may see some key of [k0, k1): a superset cut from the closed form
+// of the visible interval (query i of a sequence sees key c iff
+// c - right - (Lk - Lq) <= i <= c + left - (Lk - Lq)); exact masking happens per element.
+__device__ __forceinline__ void query_range(const MaskArgs &m, int k0, int k1, int tq, int tk, int &first, int &end) {
+    first = 0;
+    end = 0;
+    if (k1 <= k0) return;
+    if (m.kind == 2) {
+        if (m.seqs <= 0) return;
+        int sa = sequence_of(m.cu_k, m.idx_bytes, m.seqs, k0);
+        int sb = sequence_of(m.cu_k, m.idx_bytes, m.seqs, k1 - 1);
+        if (sb < 0 || sa >= m.seqs) return;
+        sa = max(sa, 0);
+        sb = min(sb, m.seqs - 1);
+        const int qa0 = load_index(m.cu_q, m.idx_bytes, sa), qa1 = load_index(m.cu_q, m.idx_bytes, sa + 1);
+        const int ka0 = load_index(m.cu_k, m.idx_bytes, sa), ka1 = load_index(m.cu_k, m.idx_bytes, sa + 1);
+        const int qb0 = load_index(m.cu_q, m.idx_bytes, sb), qb1 = load_index(m.cu_q, m.idx_bytes, sb + 1);
+        const int kb0 = load_index(m.cu_k, m.idx_bytes, sb), kb1 = load_index(m.cu_k, m.idx_bytes, sb + 1);
+        const int off_a = (ka1 - ka0) - (qa1 - qa0), off_b = (kb1 - kb0) - (qb1 - qb0);
+        first = qa0 + min(max(k0 - ka0 - m.right - off_a, 0), qa1 - qa0);
+        end = qb0 + min(max(k1 - 1 - kb0 + m.left - off_b + 1, 0), qb1 - qb0);
+    } else {
+        const int off = tk - tq;
+        first = min(max(k0 - m.right - off, 0), tq);
+        end = min(max(k1 - 1 + m.left - off + 1, 0), tq);
+    }
+    first = min(max(first, 0), tq);
+    end = min(max(end, 0), tq);
+    if (end < first) end = first;
+}
+
+struct PipeBarriers {
+    uint64_t res_full;               // the resident tiles have landed
+    uint64_t str_full[2], str_empty[2];  // streamed tiles
+    uint64_t aux_full[2];            // dkdv: per-query vectors of the step
+    uint64_t sc_full[2], sc_empty[2];    // score buffers in TMEM
+    uint64_t ps_full[2], ps_empty[2];    // P^T / dS^T (or dS) in shared memory
+    uint64_t acc_ready;
+};
+
+struct alignas(16) StepAux {  // dkdv: what the elementwise threads need per query of the step
+    float lse2[STEP];     // log-sum-exp in base 2, +inf for a query that saw no key or is out of range
+    float delta[STEP];
+    int lo[STEP], hi[STEP];
+    int clear;            // every query of the step sees every key of the block
+};
+
+struct SharedTail {
+    PipeBarriers bar;
+    StepAux aux[2];
+    uint32_t tmem_base;
+    unsigned int abort;
+    int red_lo[4], red_hi[4];
+};
+
+// shared memory: 1 KiB slack | resident A, resident B (2 x 32 KiB) | stream ring 2 x (16 + 16 KiB) |
+// P/dS ring 2 x (16 + 16 KiB) | tail
+constexpr size_t SMEM_BYTES = 1024 + 2 * BIG_BYTES + 4 * STEP_BYTES + 4 * PS_BYTES + 4096;
+
+}  // namespace
+
+// =================================================================================================
+// dK, dV
+// =================================================================================================
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                      const Sm100BwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *k_s = smem, *v_s = k_s + BIG_BYTES;
+    uint8_t *q_s = v_s + BIG_BYTES;           // [2][STEP_BYTES]
+    uint8_t *do_s = q_s + 2 * STEP_BYTES;     // [2][STEP_BYTES]
+    uint8_t *pt_s = do_s + 2 * STEP_BYTES;    // [2][PS_BYTES]
+    uint8_t *ds_s = pt_s + 2 * PS_BYTES;      // [2][PS_BYTES]
+    SharedTail &sh = *reinterpret_cast<SharedTail *>(ds_s + 2 * PS_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int group = a.hq / a.hkv;
+    const int k0 = kt * BIG, k1 = min(k0 + BIG, a.tk);
+    auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
+
+    if (threadIdx.x == 0) {
+        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_status);
+        mbar_init(BAR(sh.bar.res_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(sh.bar.str_full[i]), 1);
+            mbar_init(BAR(sh.bar.str_empty[i]), 1);
+            mbar_init(BAR(sh.bar.aux_full[i]), 32);
+            mbar_init(BAR(sh.bar.sc_full[i]), 1);
+            mbar_init(BAR(sh.bar.sc_empty[i]), 128);
+            mbar_init(BAR(sh.bar.ps_full[i]), 128);
+            mbar_init(BAR(sh.bar.ps_empty[i]), 1);
+        }
+        mbar_init(BAR(sh.bar.acc_ready), 1);
+        fence_mbar_init();
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_do);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&sh.tmem_base), 512);
+        tmem_relinquish();
+    }
+    int qfirst, qend;
+    query_range(a.mask, k0, k1, a.tq, a.tk, qfirst, qend);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh.tmem_base;
+    const bool aborted = sh.abort != 0;
+    const int q_begin = (qfirst / STEP) * STEP;
+    const int tiles = (!aborted && qend > qfirst) ? (qend - q_begin + STEP - 1) / STEP : 0;
+    const int steps = tiles * group;
+    bool failed = aborted;
+    // TMEM columns: S^T[2] at 0 / 64, dP^T[2] at 128 / 192, dV at 256, dK at 384.
+    constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
+
+    if (warp == 0) {
+        // ---------------- producer: TMA loads and the per-query vectors of each step ----------------
+        if (steps > 0) {
+            if (lane == 0) {
+                const uint32_t full = BAR(sh.bar.res_full);
+                mbar_expect_tx(full, 2 * BIG_BYTES);
+                tma_load_4d(smem_u32(k_s), &tm_k, full, 0, hk, k0, b);
+                tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, full, 64, hk, k0, b);
+                tma_load_4d(smem_u32(v_s), &tm_v, full, 0, hk, k0, b);
+                tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, full, 64, hk, k0, b);
+            }
+            for (int t = 0; t < steps; ++t) {
+                const int st = t & 1, ph = (t >> 1) & 1;
+                const int h = hk * group + t / tiles, q0 = q_begin + (t % tiles) * STEP;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1))) { failed = true; break; }
+                if (lane == 0) {
+                    const uint32_t full = BAR(sh.bar.str_full[st]);
+                    const uint32_t qd = smem_u32(q_s + st * STEP_BYTES), gd = smem_u32(do_s + st * STEP_BYTES);
+                    mbar_expect_tx(full, 2 * STEP_BYTES);
+                    tma_load_4d(qd, &tm_q, full, 0, h, q0, b);
+                    tma_load_4d(qd + STEP_HALF, &tm_q, full, 64, h, q0, b);
+                    tma_load_4d(gd, &tm_do, full, 0, h, q0, b);
+                    tma_load_4d(gd + STEP_HALF, &tm_do, full, 64, h, q0, b);
+                }
+                StepAux &aux = sh.aux[st];
+                bool clear = true;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int c = lane + 32 * i, q = q0 + c;
+                    int lo, hi;
+                    row_bounds(a.mask, q, a.tq, a.tk, lo, hi);
+                    float l2 = INFINITY, dl = 0.f;
+                    if (q < a.tq) {
+                        const int64_t at = ((int64_t)b * a.tq + q) * a.hq + h;
+                        const float x = a.lse[at];
+                        l2 = x == -INFINITY ? INFINITY : x * LOG2E;
+                        dl = a.delta[at];
+                    }
+                    aux.lse2[c] = l2;
+                    aux.delta[c] = dl;
+                    aux.lo[c] = lo;
+                    aux.hi[c] = hi;
+                    clear = clear && lo <= k0 && hi >= k0 + BIG;
+                }
+                clear = __all_sync(0xffffffffu, clear) && a.mask.kind != 1;
+                if (lane == 0) aux.clear = clear ? 1 : 0;
+                __syncwarp();
+                mbar_arrive(BAR(sh.bar.aux_full[st]));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && steps > 0) {
+            constexpr uint32_t IDESC_SC = idesc_f16(BIG, STEP, Pack<T>::FMT, 0, 0);   // [128 keys x 64 queries]
+            constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 keys x 128 d], B MN-major
+            const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            auto grads = [&](int i) -> bool {
+                const int st = i & 1, ph = (i >> 1) & 1;
+                if (!mbar_wait(BAR(sh.bar.ps_full[st]), ph)) return false;
+                tc_fence_after_sync();
+                const uint32_t pt = smem_u32(pt_s + st * PS_BYTES), ds = smem_u32(ds_s + st * PS_BYTES);
+                const uint32_t qa = smem_u32(q_s + st * STEP_BYTES), ga = smem_u32(do_s + st * STEP_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < STEP / 16; ++ks)   // dV += P^T dO over 64 queries
+                    umma_f16(tmem + COL_DV, smem_desc_sw128(pt + ks * 32, 16, 1024),
+                             smem_desc_sw128(ga + ks * 2048, STEP_HALF, 1024), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < STEP / 16; ++ks)   // dK += dS^T Q
+                    umma_f16(tmem + COL_DK, smem_desc_sw128(ds + ks * 32, 16, 1024),
+                             smem_desc_sw128(qa + ks * 2048, STEP_HALF, 1024), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(BAR(sh.bar.str_empty[st]));
+                umma_commit(BAR(sh.bar.ps_empty[st]));
+                return true;
+            };
+            if (!mbar_wait(BAR(sh.bar.res_full), 0)) failed = true;
+            for (int t = 0; t < steps && !failed; ++t) {
+                const int st = t & 1, ph = (t >> 1) & 1;
+                if (!mbar_wait(BAR(sh.bar.str_full[st]), ph) || !mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1)) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t qa = smem_u32(q_s + st * STEP_BYTES), ga = smem_u32(do_s + st * STEP_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
+                    umma_f16(tmem + COL_ST + st * STEP,
+                             smem_desc_sw128(k_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
+                             smem_desc_sw128(qa + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
+                    umma_f16(tmem + COL_DPT + st * STEP,
+                             smem_desc_sw128(v_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
+                             smem_desc_sw128(ga + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+                umma_commit(BAR(sh.bar.sc_full[st]));
+                if (t > 0 && !grads(t - 1)) { failed = true; break; }
+            }
+            if (!failed && !grads(steps - 1)) failed = true;
+            if (!failed) umma_commit(BAR(sh.bar.acc_ready));
+        }
+    } else {
+        // ---------------- elementwise: one key row per thread ----------------
+        const int lane_base = 32 * (warp & 3);
+        const int r = lane_base + lane;
+        const int key = k0 + r;
+        const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
+        const bool open = key < a.tk && !key_padded(a.mask, b, key);
+        for (int t = 0; t < steps && !failed; ++t) {
+            const int st = t & 1, ph = (t >> 1) & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.aux_full[st]), ph) && mbar_wait(BAR(sh.bar.sc_full[st]), ph))) {
+                failed = true;
+                break;
+            }
+            tc_fence_after_sync();
+            float s[STEP], dp[STEP];
+            tmem_ld32(t_lane + COL_ST + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + COL_ST + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            tmem_ld32(t_lane + COL_DPT + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+            tmem_ld32(t_lane + COL_DPT + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            mbar_arrive(BAR(sh.bar.sc_empty[st]));
+
+            const StepAux &aux = sh.aux[st];
+            const bool masked = aux.clear == 0;
+#pragma unroll
+            for (int c4 = 0; c4 < STEP / 4; ++c4) {
+                const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[c4 * 4]);
+                const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[c4 * 4]);
+                const float l2v[4] = {l2.x, l2.y, l2.z, l2.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = c4 * 4 + e;
+                    float p = ex2(fmaf(s[c], a.scale_log2, -l2v[e]));
+                    if (masked) p = (open && key >= aux.lo[c] && key < aux.hi[c]) ? p : 0.f;
+                    s[c] = p;
+                    dp[c] = p * (dp[c] - dlv[e]);
+                }
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
+            store_row64<T>(pt_s + st * PS_BYTES, r, s);
+            store_row64<T>(ds_s + st * PS_BYTES, r, dp);
+            fence_proxy_async_smem();
+            mbar_arrive(BAR(sh.bar.ps_full[st]));
+        }
+        // ---------------- epilogue ----------------
+        T *dk = static_cast<T *>(a.dk) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD;
+        T *dv = static_cast<T *>(a.dv) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD;
+        if (steps == 0 || failed) {
+            if (key < a.tk && !failed) {
+                store_zero_row(dk);
+                store_zero_row(dv);
+            }
+        } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
+            tc_fence_after_sync();
+            store_acc_row<T>(t_lane + COL_DV, dv, 1.f, key < a.tk);
+            store_acc_row<T>(t_lane + COL_DK, dk, a.scale, key < a.tk);
+            tc_fence_before_sync();
+        } else {
+            failed = true;
+        }
+    }
+
+    if (failed && !aborted) atomicOr(&g_sm100_status, 2u);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// =================================================================================================
+// dQ
+// =================================================================================================
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                    const Sm100BwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *q_s = smem, *do_s = q_s + BIG_BYTES;
+    uint8_t *k_s = do_s + BIG_BYTES;          // [2][STEP_BYTES]
+    uint8_t *v_s = k_s + 2 * STEP_BYTES;      // [2][STEP_BYTES]
+    uint8_t *ds_s = v_s + 2 * STEP_BYTES;     // [2][PS_BYTES]
+    SharedTail &sh = *reinterpret_cast<SharedTail *>(ds_s + 4 * PS_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x;
+    const int qt = gridDim.y - 1 - blockIdx.y;
+    const int b = blockIdx.z;
+    const int hk = h / (a.hq / a.hkv);
+    const int m0 = qt * BIG;
+    auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
+
+    if (threadIdx.x == 0) {
+        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_status);
+        mbar_init(BAR(sh.bar.res_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(BAR(sh.bar.str_full[i]), 1);
+            mbar_init(BAR(sh.bar.str_empty[i]), 1);
+            mbar_init(BAR(sh.bar.aux_full[i]), 1);
+            mbar_init(BAR(sh.bar.sc_full[i]), 1);
+            mbar_init(BAR(sh.bar.sc_empty[i]), 128);
+            mbar_init(BAR(sh.bar.ps_full[i]), 128);
+            mbar_init(BAR(sh.bar.ps_empty[i]), 1);
+        }
+        mbar_init(BAR(sh.bar.acc_ready), 1);
+        fence_mbar_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_do);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&sh.tmem_base), 512);
+        tmem_relinquish();
+    }
+    const int sw = warp - 2;
+    const int lane_base = 32 * (warp & 3);
+    const int r = lane_base + lane;
+    int lo = a.tk, hi = 0;
+    if (warp >= 2) {
+        row_bounds(a.mask, m0 + r, a.tq, a.tk, lo, hi);
+        int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
+        if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh.tmem_base;
+    const bool aborted = sh.abort != 0;
+    int kmin = a.tk, kmax = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { kmin = min(kmin, sh.red_lo[i]); kmax = max(kmax, sh.red_hi[i]); }
+    const int steps = (!aborted && kmax > kmin) ? (kmax - kmin + STEP - 1) / STEP : 0;
+    bool failed = aborted;
+    // TMEM columns: S[2] at 0 / 64, dP[2] at 128 / 192, dQ at 256.
+    constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
+
+    if (warp == 0) {
+        if (lane == 0 && steps > 0) {
+            const uint32_t full = BAR(sh.bar.res_full);
+            mbar_expect_tx(full, 2 * BIG_BYTES);
+            tma_load_4d(smem_u32(q_s), &tm_q, full, 0, h, m0, b);
+            tma_load_4d(smem_u32(q_s + BIG_HALF), &tm_q, full, 64, h, m0, b);
+            tma_load_4d(smem_u32(do_s), &tm_do, full, 0, h, m0, b);
+            tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
+            for (int t = 0; t < steps; ++t) {
+                const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * STEP;
+                if (!mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t sf = BAR(sh.bar.str_full[st]);
+                const uint32_t kd = smem_u32(k_s + st * STEP_BYTES), vd = smem_u32(v_s + st * STEP_BYTES);
+                mbar_expect_tx(sf, 2 * STEP_BYTES);
+                tma_load_4d(kd, &tm_k, sf, 0, hk, c0, b);
+                tma_load_4d(kd + STEP_HALF, &tm_k, sf, 64, hk, c0, b);
+                tma_load_4d(vd, &tm_v, sf, 0, hk, c0, b);
+                tma_load_4d(vd + STEP_HALF, &tm_v, sf, 64, hk, c0, b);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && steps > 0) {
+            constexpr uint32_t IDESC_SC = idesc_f16(BIG, STEP, Pack<T>::FMT, 0, 0);   // [128 queries x 64 keys]
+            constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 queries x 128 d]
+            const uint32_t q_addr = smem_u32(q_s), g_addr = smem_u32(do_s);
+            auto grads = [&](int i) -> bool {
+                const int st = i & 1, ph = (i >> 1) & 1;
+                if (!mbar_wait(BAR(sh.bar.ps_full[st]), ph)) return false;
+                tc_fence_after_sync();
+                const uint32_t ds = smem_u32(ds_s + st * PS_BYTES), ka = smem_u32(k_s + st * STEP_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < STEP / 16; ++ks)   // dQ += dS K over 64 keys
+                    umma_f16(tmem + COL_DQ, smem_desc_sw128(ds + ks * 32, 16, 1024),
+                             smem_desc_sw128(ka + ks * 2048, STEP_HALF, 1024), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(BAR(sh.bar.str_empty[st]));
+                umma_commit(BAR(sh.bar.ps_empty[st]));
+                return true;
+            };
+            if (!mbar_wait(BAR(sh.bar.res_full), 0)) failed = true;
+            for (int t = 0; t < steps && !failed; ++t) {
+                const int st = t & 1, ph = (t >> 1) & 1;
+                if (!mbar_wait(BAR(sh.bar.str_full[st]), ph) || !mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1)) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t ka = smem_u32(k_s + st * STEP_BYTES), va = smem_u32(v_s + st * STEP_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)   // S = Q K^T
+                    umma_f16(tmem + COL_S + st * STEP,
+                             smem_desc_sw128(q_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
+                             smem_desc_sw128(ka + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)   // dP = dO V^T
+                    umma_f16(tmem + COL_DP + st * STEP,
+                             smem_desc_sw128(g_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
+                             smem_desc_sw128(va + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+                umma_commit(BAR(sh.bar.sc_full[st]));
+                if (t > 0 && !grads(t - 1)) { failed = true; break; }
+            }
+            if (!failed && !grads(steps - 1)) failed = true;
+            if (!failed) umma_commit(BAR(sh.bar.acc_ready));
+        }
+    } else {
+        // ---------------- elementwise: one query row per thread ----------------
+        const int row = m0 + r;
+        const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
+        const bool padded = a.mask.kind == 1;
+        float l2 = INFINITY, dl = 0.f;
+        if (row < a.tq) {
+            const int64_t at = ((int64_t)b * a.tq + row) * a.hq + h;
+            const float x = a.lse[at];
+            l2 = x == -INFINITY ? INFINITY : x * LOG2E;
+            dl = a.delta[at];
+        }
+        for (int t = 0; t < steps && !failed; ++t) {
+            const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * STEP;
+            uint32_t pb[2] = {0, 0};
+            if (padded) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int key = c0 + i * 32 + lane;
+                    pb[i] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
+                }
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.sc_full[st]), ph))) { failed = true; break; }
+            tc_fence_after_sync();
+            float s[STEP], dp[STEP];
+            tmem_ld32(t_lane + COL_S + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + COL_S + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            tmem_ld32(t_lane + COL_DP + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+            tmem_ld32(t_lane + COL_DP + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            mbar_arrive(BAR(sh.bar.sc_empty[st]));
+
+            const bool clear = !padded && c0 >= lo && c0 + STEP <= hi;
+            const bool masked = !__all_sync(0xffffffffu, clear);
+#pragma unroll
+            for (int c = 0; c < STEP; ++c) {
+                float p = ex2(fmaf(s[c], a.scale_log2, -l2));
+                if (masked) {
+                    const int key = c0 + c;
+                    p = (key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u)) ? p : 0.f;
+                }
+                dp[c] = p * (dp[c] - dl);
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
+            store_row64<T>(ds_s + st * PS_BYTES, r, dp);
+            fence_proxy_async_smem();
+            mbar_arrive(BAR(sh.bar.ps_full[st]));
+        }
+        T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD;
+        if (steps == 0 || failed) {
+            if (row < a.tq && !failed) store_zero_row(dq);
+        } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
+            tc_fence_after_sync();
+            store_acc_row<T>(t_lane + COL_DQ, dq, a.scale, row < a.tq);
+            tc_fence_before_sync();
+        } else {
+            failed = true;
+        }
+    }
+
+    if (failed && !aborted) atomicOr(&g_sm100_status, 4u);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+template <typename T>
+static cudaError_t launch_t(const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
+    bwd_dq_sm100_kernel<T><<<gq, THREADS, SMEM_BYTES, stream>>>(m.q128, m.do128, m.k64, m.v64, a);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    dim3 gk((a.tk + BIG - 1) / BIG, a.hkv, a.b);
+    bwd_dkdv_sm100_kernel<T><<<gk, THREADS, SMEM_BYTES, stream>>>(m.k128, m.v128, m.q64, m.do64, a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream) {
+    return dtype == DASH_ATTN_BF16 ? launch_t<__nv_bfloat16>(m, a, stream) : launch_t<__half>(m, a, stream);
+}
+
+}  // namespace dash

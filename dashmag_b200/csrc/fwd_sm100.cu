@@ -251,9 +251,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     s[c] = vis ? s[c] : -INFINITY;
                 }
             }
-            float mx = s[0];
+            // Row maximum: eight independent chains of three-input maxima, then a tree.
+            float mx8[8];
 #pragma unroll
-            for (int c = 1; c < BN; ++c) mx = fmaxf(mx, s[c]);
+            for (int e = 0; e < 8; ++e) mx8[e] = fmax3(s[e], s[8 + e], s[16 + e]);
+#pragma unroll
+            for (int c = 24; c < BN; c += 16)
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    mx8[e] = c + 8 + e < BN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
+            const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
             // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8.
             float factor = 1.f;
             bool rescale = false;
@@ -270,21 +277,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // The P buffer is free once P V of tile j - 2 has completed.
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_empty, st), ph ^ 1))) { failed = true; break; }
             uint8_t *p_row = p_s + st * TILE_BYTES + r * 128;
-            float sum = 0.f;
+            const float2 sl2 = make_float2(a.scale_log2, a.scale_log2), neg2 = make_float2(neg, neg);
+            float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
             for (int cc = 0; cc < BN / 8; ++cc) {
                 float p[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    p[e] = ex2(fmaf(s[cc * 8 + e], a.scale_log2, neg));
-                    sum += p[e];
+                for (int e = 0; e < 4; ++e) {
+                    // two exponents per packed FMA, four independent packed sums
+                    const float2 x = fma2(make_float2(s[cc * 8 + 2 * e], s[cc * 8 + 2 * e + 1]), sl2, neg2);
+                    p[2 * e] = ex2(x.x);
+                    p[2 * e + 1] = ex2(x.y);
+                    sum2[e] = add2(sum2[e], make_float2(p[2 * e], p[2 * e + 1]));
                 }
                 uint4 v = make_uint4(Pack<T>::two(p[0], p[1]), Pack<T>::two(p[2], p[3]), Pack<T>::two(p[4], p[5]),
                                      Pack<T>::two(p[6], p[7]));
                 // 16-byte chunk (cc mod 8) of the row's 128 bytes in half (cc / 8), XOR-swizzled by the row.
                 *reinterpret_cast<uint4 *>(p_row + (cc >> 3) * HALF_BYTES + (((cc & 7) ^ (r & 7)) << 4)) = v;
             }
-            l += sum;
+            {
+                const float2 t = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+                l += t.x + t.y;
+            }
 
             // O holds tiles 0..j-1 once P V of tile j - 1 has completed; rescale it before P V of tile j.
             if (j > 0) {

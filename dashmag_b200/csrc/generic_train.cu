@@ -521,6 +521,24 @@ static cudaError_t backward_t(const TrainArgs &a, cudaStream_t stream, int *laun
     return cudaSuccess;
 }
 
+template <typename T>
+static cudaError_t delta_t(const TrainArgs &a, cudaStream_t stream, int *launches) {
+    int64_t rows = (int64_t)a.b * a.tq * a.hq;
+    unsigned blocks = (unsigned)((rows + THREADS / 32 - 1) / (THREADS / 32));
+    generic_delta_kernel<T><<<blocks, THREADS, 0, stream>>>(a);
+    *launches += 1;
+    return cudaGetLastError();
+}
+
+// delta = rowsum(dO * O) alone, for the tensor-core backward.
+cudaError_t launch_generic_delta(int dtype, const TrainArgs &a, cudaStream_t stream, int *launches) {
+    switch (dtype) {
+        case 0: return delta_t<float>(a, stream, launches);
+        case 1: return delta_t<__nv_bfloat16>(a, stream, launches);
+        default: return delta_t<__half>(a, stream, launches);
+    }
+}
+
 cudaError_t launch_generic_forward(int dtype, const TrainArgs &a, cudaStream_t stream, int *launches) {
     switch (dtype) {
         case 0: return forward_t<float>(a, stream, launches);

@@ -10,6 +10,7 @@ struct DecodeArgs;
 // Each adds the kernels it launched to *launches and returns the first launch error.
 cudaError_t launch_generic_forward(int dtype, const TrainArgs &a, cudaStream_t stream, int *launches);
 cudaError_t launch_generic_backward(int dtype, const TrainArgs &a, cudaStream_t stream, int *launches);
+cudaError_t launch_generic_delta(int dtype, const TrainArgs &a, cudaStream_t stream, int *launches);
 cudaError_t launch_decode(int dtype, const DecodeArgs &a, bool vector_ok, cudaStream_t stream, int *launches);
 // The library's own decode scratch: its size in floats, and its address on the current device.
 size_t decode_static_capacity_floats();

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "launch.h"
 #include "sm100_kernels.h"
 
 namespace dash {
@@ -63,7 +64,7 @@ bool tma_readable(const void *ptr, const int64_t *stride) {
 
 // A [B, T, H, 128] tensor of 16-bit elements as a 4-D map (d, h, t, b) with boxes of 64 x 1 x 128 x 1
 // and the 128-byte swizzle: each load brings 128 rows of 128 bytes of one head.
-bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride) {
+bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows = 128) {
     EncodeTiled fn = encoder();
     if (!fn) return false;
     auto bytes = [](int64_t elems) { return static_cast<cuuint64_t>(elems) * 2; };
@@ -72,7 +73,7 @@ bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, c
     cuuint64_t strides[3] = {h > 1 ? bytes(stride[2]) : 256, t > 1 ? bytes(stride[1]) : 256, b > 1 ? bytes(stride[0]) : 256};
     for (cuuint64_t s : strides)
         if (s == 0 || s % 16 != 0 || s >= (1ull << 40)) return false;
-    cuuint32_t box[4] = {64, 1, 128, 1};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
     cuuint32_t elem[4] = {1, 1, 1, 1};
     CUtensorMapDataType dt = dtype == DASH_ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -87,7 +88,7 @@ float resolved_scale(const dash_attn_params *p) {
 }  // namespace
 
 bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
-    if (backward) return false;  // the backward runs the generic kernels
+    if (backward && !tma_readable(q, p->do_stride)) return false;  // dO's strides; its base is checked at launch
     if (p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16) return false;
     if (p->d != 128) return false;
     const float scale = resolved_scale(p);
@@ -123,10 +124,36 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     return e;
 }
 
-cudaError_t sm100_backward(const dash_attn_params *, const TrainArgs &, void *, cudaStream_t, int *, bool *,
-                           std::string &err) {
-    err = "attention_backward: the tensor-core path has no backward";
-    return cudaSuccess;
+cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *, cudaStream_t stream, int *launches,
+                           bool *atomic, std::string &err) {
+    *atomic = false;  // both kernels sum in a fixed order whatever `deterministic` says
+    Sm100BwdMaps m;
+    const void *q = a.q.ptr, *k = a.k.ptr, *v = a.v.ptr, *g = a.dout.ptr;
+    bool ok = encode(&m.q128, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 128) &&
+              encode(&m.do128, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 128) &&
+              encode(&m.k64, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 64) &&
+              encode(&m.v64, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 64) &&
+              encode(&m.k128, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 128) &&
+              encode(&m.v128, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 128) &&
+              encode(&m.q64, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 64) &&
+              encode(&m.do64, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 64);
+    if (!ok) {
+        err = "attention_backward: the driver refused a TMA tensor map over the inputs";
+        return cudaSuccess;
+    }
+    cudaError_t e = launch_generic_delta(p->dtype, a, stream, launches);
+    if (e != cudaSuccess) return e;
+    Sm100BwdArgs f{};
+    f.b = p->b; f.tq = p->tq; f.tk = p->tk; f.hq = p->hq; f.hkv = p->hkv;
+    f.scale = a.scale;
+    f.scale_log2 = a.scale * 1.4426950408889634f;
+    f.lse = a.lse;
+    f.delta = a.delta;
+    f.dq = a.dq; f.dk = a.dk; f.dv = a.dv;
+    f.mask = a.mask;
+    e = launch_bwd_sm100(p->dtype, m, f, stream);
+    *launches += 2;
+    return e;
 }
 
 }  // namespace dash

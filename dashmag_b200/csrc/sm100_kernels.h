@@ -17,6 +17,24 @@ struct Sm100FwdArgs {
     MaskArgs mask;
 };
 
+struct Sm100BwdArgs {
+    int b, tq, tk, hq, hkv;
+    float scale, scale_log2;
+    const float *lse;    // [B,Tq,Hq], the forward's
+    const float *delta;  // [B,Tq,Hq], rowsum(dO * O)
+    void *dq, *dk, *dv;  // contiguous, the inputs' dtype
+    MaskArgs mask;
+};
+
+// Tensor maps of the backward: each tensor once with boxes of 128 rows (the tile a block keeps)
+// and once with boxes of 64 rows (the tiles it streams).
+struct Sm100BwdMaps {
+    CUtensorMap q128, do128, k64, v64;   // dq kernel
+    CUtensorMap k128, v128, q64, do64;   // dkdv kernel
+};
+
+cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream);
+
 cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                              const Sm100FwdArgs &a, cudaStream_t stream);
 // Reads (and optionally clears) the sticky device word the kernels raise when a bounded wait ran
