@@ -6,10 +6,12 @@ module raises at import time of the first call, naming the build command.
 from __future__ import annotations
 
 import ctypes
+import os
 import pathlib
 
 HERE = pathlib.Path(__file__).resolve().parent
-LIB_PATH = HERE / "csrc" / "libdash_attn_b200.so"
+#: The built library; DASH_ATTN_LIBRARY names another build of the same sources (for experiments).
+LIB_PATH = pathlib.Path(os.environ.get("DASH_ATTN_LIBRARY", HERE / "csrc" / "libdash_attn_b200.so"))
 
 OK, INVALID, UNSUPPORTED, WORKSPACE, CUDA = 0, 1, 2, 3, 4
 MASK_NONE, MASK_KEY_PADDING, MASK_PACKED = 0, 1, 2

@@ -32,7 +32,10 @@ namespace dash {
 
 using namespace ptx;
 
-extern __device__ unsigned int g_sm100_status;
+// Sticky, like the forward's: non-zero once a bounded wait of these kernels has run out.  (Without
+// relocatable device code every translation unit owns its device variables, so the backward has a
+// word of its own and the host reads both.)
+__device__ unsigned int g_sm100_bwd_status = 0;
 
 namespace {
 
@@ -44,7 +47,8 @@ constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes
 constexpr int STEP_BYTES = STEP * HD * 2;  // 16 KiB
 constexpr int STEP_HALF = STEP_BYTES / 2;  // 64 rows of 128 bytes
 constexpr int PS_BYTES = BIG * STEP * 2;   // 16 KiB: a P^T / dS^T / dS tile, 128 rows of 128 bytes
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;        // dq
+constexpr int THREADS_DKDV = 224;   // dkdv: one more warp gathers the per-query vectors
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <typename T> struct Pack;
@@ -171,7 +175,7 @@ constexpr size_t SMEM_BYTES = 1024 + 2 * BIG_BYTES + 4 * STEP_BYTES + 4 * PS_BYT
 // dK, dV
 // =================================================================================================
 template <typename T>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS_DKDV, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const Sm100BwdArgs a) {
@@ -191,7 +195,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
 
     if (threadIdx.x == 0) {
-        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_status);
+        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
         mbar_init(BAR(sh.bar.res_full), 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(sh.bar.str_full[i]), 1);
@@ -228,54 +232,58 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
 
     if (warp == 0) {
-        // ---------------- producer: TMA loads and the per-query vectors of each step ----------------
-        if (steps > 0) {
-            if (lane == 0) {
-                const uint32_t full = BAR(sh.bar.res_full);
-                mbar_expect_tx(full, 2 * BIG_BYTES);
-                tma_load_4d(smem_u32(k_s), &tm_k, full, 0, hk, k0, b);
-                tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, full, 64, hk, k0, b);
-                tma_load_4d(smem_u32(v_s), &tm_v, full, 0, hk, k0, b);
-                tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, full, 64, hk, k0, b);
-            }
+        // ---------------- producer: TMA loads ----------------
+        if (lane == 0 && steps > 0) {
+            const uint32_t rfull = BAR(sh.bar.res_full);
+            mbar_expect_tx(rfull, 2 * BIG_BYTES);
+            tma_load_4d(smem_u32(k_s), &tm_k, rfull, 0, hk, k0, b);
+            tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, rfull, 64, hk, k0, b);
+            tma_load_4d(smem_u32(v_s), &tm_v, rfull, 0, hk, k0, b);
+            tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, rfull, 64, hk, k0, b);
             for (int t = 0; t < steps; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1;
                 const int h = hk * group + t / tiles, q0 = q_begin + (t % tiles) * STEP;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1))) { failed = true; break; }
-                if (lane == 0) {
-                    const uint32_t full = BAR(sh.bar.str_full[st]);
-                    const uint32_t qd = smem_u32(q_s + st * STEP_BYTES), gd = smem_u32(do_s + st * STEP_BYTES);
-                    mbar_expect_tx(full, 2 * STEP_BYTES);
-                    tma_load_4d(qd, &tm_q, full, 0, h, q0, b);
-                    tma_load_4d(qd + STEP_HALF, &tm_q, full, 64, h, q0, b);
-                    tma_load_4d(gd, &tm_do, full, 0, h, q0, b);
-                    tma_load_4d(gd + STEP_HALF, &tm_do, full, 64, h, q0, b);
-                }
-                StepAux &aux = sh.aux[st];
-                bool clear = true;
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int c = lane + 32 * i, q = q0 + c;
-                    int lo, hi;
-                    row_bounds(a.mask, q, a.tq, a.tk, lo, hi);
-                    float l2 = INFINITY, dl = 0.f;
-                    if (q < a.tq) {
-                        const int64_t at = ((int64_t)b * a.tq + q) * a.hq + h;
-                        const float x = a.lse[at];
-                        l2 = x == -INFINITY ? INFINITY : x * LOG2E;
-                        dl = a.delta[at];
-                    }
-                    aux.lse2[c] = l2;
-                    aux.delta[c] = dl;
-                    aux.lo[c] = lo;
-                    aux.hi[c] = hi;
-                    clear = clear && lo <= k0 && hi >= k0 + BIG;
-                }
-                clear = __all_sync(0xffffffffu, clear) && a.mask.kind != 1;
-                if (lane == 0) aux.clear = clear ? 1 : 0;
-                __syncwarp();
-                mbar_arrive(BAR(sh.bar.aux_full[st]));
+                if (!mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t full = BAR(sh.bar.str_full[st]);
+                const uint32_t qd = smem_u32(q_s + st * STEP_BYTES), gd = smem_u32(do_s + st * STEP_BYTES);
+                mbar_expect_tx(full, 2 * STEP_BYTES);
+                tma_load_4d(qd, &tm_q, full, 0, h, q0, b);
+                tma_load_4d(qd + STEP_HALF, &tm_q, full, 64, h, q0, b);
+                tma_load_4d(gd, &tm_do, full, 0, h, q0, b);
+                tma_load_4d(gd + STEP_HALF, &tm_do, full, 64, h, q0, b);
             }
+        }
+    } else if (warp == 6) {
+        // ---------------- the per-query vectors of each step: log-sum-exp, delta, key interval ----------------
+        for (int t = 0; t < steps; ++t) {
+            const int st = t & 1, ph = (t >> 1) & 1;
+            const int h = hk * group + t / tiles, q0 = q_begin + (t % tiles) * STEP;
+            // aux[st] is free when the stage is: the elementwise threads of step t - 2 are done with it.
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1))) { failed = true; break; }
+            StepAux &aux = sh.aux[st];
+            bool clear = true;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c = lane + 32 * i, q = q0 + c;
+                int lo, hi;
+                row_bounds(a.mask, q, a.tq, a.tk, lo, hi);
+                float l2 = INFINITY, dl = 0.f;
+                if (q < a.tq) {
+                    const int64_t at = ((int64_t)b * a.tq + q) * a.hq + h;
+                    const float x = a.lse[at];
+                    l2 = x == -INFINITY ? INFINITY : x * LOG2E;
+                    dl = a.delta[at];
+                }
+                aux.lse2[c] = l2;
+                aux.delta[c] = dl;
+                aux.lo[c] = lo;
+                aux.hi[c] = hi;
+                clear = clear && lo <= k0 && hi >= k0 + BIG;
+            }
+            clear = __all_sync(0xffffffffu, clear) && a.mask.kind != 1;
+            if (lane == 0) aux.clear = clear ? 1 : 0;
+            __syncwarp();
+            mbar_arrive(BAR(sh.bar.aux_full[st]));
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -291,12 +299,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 const uint32_t qa = smem_u32(q_s + st * STEP_BYTES), ga = smem_u32(do_s + st * STEP_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < STEP / 16; ++ks)   // dV += P^T dO over 64 queries
-                    umma_f16(tmem + COL_DV, smem_desc_sw128(pt + ks * 32, 16, 1024),
-                             smem_desc_sw128(ga + ks * 2048, STEP_HALF, 1024), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_f16(tmem + COL_DV, desc_at(smem_desc_sw128(pt, 16, 1024), ks * 32),
+                             desc_at(smem_desc_sw128(ga, STEP_HALF, 1024), ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < STEP / 16; ++ks)   // dK += dS^T Q
-                    umma_f16(tmem + COL_DK, smem_desc_sw128(ds + ks * 32, 16, 1024),
-                             smem_desc_sw128(qa + ks * 2048, STEP_HALF, 1024), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_f16(tmem + COL_DK, desc_at(smem_desc_sw128(ds, 16, 1024), ks * 32),
+                             desc_at(smem_desc_sw128(qa, STEP_HALF, 1024), ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(BAR(sh.bar.str_empty[st]));
                 umma_commit(BAR(sh.bar.ps_empty[st]));
                 return true;
@@ -313,13 +321,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
                     umma_f16(tmem + COL_ST + st * STEP,
-                             smem_desc_sw128(k_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
-                             smem_desc_sw128(qa + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+                             desc_at(smem_desc_sw128(k_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                             desc_at(smem_desc_sw128(qa, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
                     umma_f16(tmem + COL_DPT + st * STEP,
-                             smem_desc_sw128(v_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
-                             smem_desc_sw128(ga + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+                             desc_at(smem_desc_sw128(v_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                             desc_at(smem_desc_sw128(ga, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
                 umma_commit(BAR(sh.bar.sc_full[st]));
                 if (t > 0 && !grads(t - 1)) { failed = true; break; }
             }
@@ -350,7 +358,14 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             mbar_arrive(BAR(sh.bar.sc_empty[st]));
 
             const StepAux &aux = sh.aux[st];
-            const bool masked = aux.clear == 0;
+            if (aux.clear == 0) {
+                // A step that cuts some query's interval (or has padded keys): hide what this key
+                // is not seen by before the exponentials, in a pass of its own so that the common,
+                // unmasked step pays nothing for it.
+#pragma unroll
+                for (int c = 0; c < STEP; ++c)
+                    s[c] = (open && key >= aux.lo[c] && key < aux.hi[c]) ? s[c] : -INFINITY;
+            }
 #pragma unroll
             for (int c4 = 0; c4 < STEP / 4; ++c4) {
                 const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[c4 * 4]);
@@ -359,8 +374,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int c = c4 * 4 + e;
-                    float p = ex2(fmaf(s[c], a.scale_log2, -l2v[e]));
-                    if (masked) p = (open && key >= aux.lo[c] && key < aux.hi[c]) ? p : 0.f;
+                    const float p = ex2(fmaf(s[c], a.scale_log2, -l2v[e]));
                     s[c] = p;
                     dp[c] = p * (dp[c] - dlv[e]);
                 }
@@ -389,7 +403,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     }
 
-    if (failed && !aborted) atomicOr(&g_sm100_status, 2u);
+    if (failed && !aborted) atomicOr(&g_sm100_bwd_status, 2u);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -423,7 +437,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
 
     if (threadIdx.x == 0) {
-        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_status);
+        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
         mbar_init(BAR(sh.bar.res_full), 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(sh.bar.str_full[i]), 1);
@@ -499,8 +513,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const uint32_t ds = smem_u32(ds_s + st * PS_BYTES), ka = smem_u32(k_s + st * STEP_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < STEP / 16; ++ks)   // dQ += dS K over 64 keys
-                    umma_f16(tmem + COL_DQ, smem_desc_sw128(ds + ks * 32, 16, 1024),
-                             smem_desc_sw128(ka + ks * 2048, STEP_HALF, 1024), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_f16(tmem + COL_DQ, desc_at(smem_desc_sw128(ds, 16, 1024), ks * 32),
+                             desc_at(smem_desc_sw128(ka, STEP_HALF, 1024), ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(BAR(sh.bar.str_empty[st]));
                 umma_commit(BAR(sh.bar.ps_empty[st]));
                 return true;
@@ -517,13 +531,13 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)   // S = Q K^T
                     umma_f16(tmem + COL_S + st * STEP,
-                             smem_desc_sw128(q_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
-                             smem_desc_sw128(ka + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+                             desc_at(smem_desc_sw128(q_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                             desc_at(smem_desc_sw128(ka, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)   // dP = dO V^T
                     umma_f16(tmem + COL_DP + st * STEP,
-                             smem_desc_sw128(g_addr + (ks >> 2) * BIG_HALF + (ks & 3) * 32, 16, 1024),
-                             smem_desc_sw128(va + (ks >> 2) * STEP_HALF + (ks & 3) * 32, 16, 1024), IDESC_SC, ks > 0 ? 1u : 0u);
+                             desc_at(smem_desc_sw128(g_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                             desc_at(smem_desc_sw128(va, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
                 umma_commit(BAR(sh.bar.sc_full[st]));
                 if (t > 0 && !grads(t - 1)) { failed = true; break; }
             }
@@ -564,14 +578,16 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             mbar_arrive(BAR(sh.bar.sc_empty[st]));
 
             const bool clear = !padded && c0 >= lo && c0 + STEP <= hi;
-            const bool masked = !__all_sync(0xffffffffu, clear);
+            if (!__all_sync(0xffffffffu, clear)) {
+#pragma unroll
+                for (int c = 0; c < STEP; ++c) {
+                    const int key = c0 + c;
+                    s[c] = (key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u)) ? s[c] : -INFINITY;
+                }
+            }
 #pragma unroll
             for (int c = 0; c < STEP; ++c) {
-                float p = ex2(fmaf(s[c], a.scale_log2, -l2));
-                if (masked) {
-                    const int key = c0 + c;
-                    p = (key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u)) ? p : 0.f;
-                }
+                const float p = ex2(fmaf(s[c], a.scale_log2, -l2));
                 dp[c] = p * (dp[c] - dl);
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
@@ -591,7 +607,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
     }
 
-    if (failed && !aborted) atomicOr(&g_sm100_status, 4u);
+    if (failed && !aborted) atomicOr(&g_sm100_bwd_status, 4u);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -611,8 +627,18 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaSt
     bwd_dq_sm100_kernel<T><<<gq, THREADS, SMEM_BYTES, stream>>>(m.q128, m.do128, m.k64, m.v64, a);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     dim3 gk((a.tk + BIG - 1) / BIG, a.hkv, a.b);
-    bwd_dkdv_sm100_kernel<T><<<gk, THREADS, SMEM_BYTES, stream>>>(m.k128, m.v128, m.q64, m.do64, a);
+    bwd_dkdv_sm100_kernel<T><<<gk, THREADS_DKDV, SMEM_BYTES, stream>>>(m.k128, m.v128, m.q64, m.do64, a);
     return cudaGetLastError();
+}
+
+cudaError_t read_sm100_bwd_status(unsigned int *status, bool clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_sm100_bwd_status, sizeof(unsigned int));
+    if (e != cudaSuccess) return e;
+    if (clear && *status) {
+        unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_sm100_bwd_status, &zero, sizeof(unsigned int));
+    }
+    return e;
 }
 
 cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream) {

@@ -1,8 +1,9 @@
 // The training forward on the 5th-generation tensor cores: bf16 / f16, head dimension 128.
 //
-// One block of 192 threads per (tile of 128 queries, query head):
-//   warp 0      one lane issues the TMA tile loads: the Q tile once, then K and V tiles of 128 keys
-//               into two-stage rings of 128-byte-swizzled shared memory;
+// One block of 224 threads per (tile of 128 queries, query head):
+//   warp 0, 6   one lane each issues the TMA tile loads: warp 0 the Q tile once and then the K
+//               tiles of 128 keys, warp 6 the V tiles, into two-stage rings of 128-byte-swizzled
+//               shared memory;
 //   warp 1      owns tensor memory (512 columns: two S buffers and the O accumulator) and one lane
 //               issues the tcgen05 MMAs: S_j = Q K_j^T into the S buffer (j mod 2), O += P_j V_j;
 //   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S_j from tensor
@@ -43,7 +44,7 @@ constexpr int BN = 128;          // keys per tile
 constexpr int HD = 128;          // head dimension
 constexpr int TILE_BYTES = BM * HD * 2;  // 32 KiB: any of the Q, K, V, P tiles
 constexpr int HALF_BYTES = TILE_BYTES / 2;  // one 64-column half: 128 rows of 128 bytes
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;
 constexpr float RESCALE_LOG2 = 8.0f;
 
 struct Barriers {
@@ -129,7 +130,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int lane_base = 32 * (warp & 3);         // the TMEM lanes this warp may touch
     const int r = lane_base + lane;                // row of the tile (softmax threads)
     int lo = a.tk, hi = 0;
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
         row_bounds(a.mask, m0 + r, a.tq, a.tk, lo, hi);
         int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
         if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
@@ -160,9 +161,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 mbar_expect_tx(full, TILE_BYTES);
                 tma_load_4d(dst, &tm_k, full, 0, hk, k0, b);
                 tma_load_4d(dst + HALF_BYTES, &tm_k, full, 64, hk, k0, b);
+            }
+        }
+    } else if (warp == 6) {
+        // ---------------- TMA producer of the V ring (its own warp: a K tile is wanted long
+        // before the V tile of the same keys, and neither load should queue behind the other) ----
+        if (lane == 0 && n_tiles > 0) {
+            for (int j = 0; j < n_tiles && !failed; ++j) {
+                const int st = j & 1, ph = (j >> 1) & 1, k0 = kmin + j * BN;
                 if (!mbar_wait(BAR(sh.bar.v_empty, st), ph ^ 1)) { failed = true; break; }
-                full = BAR(sh.bar.v_full, st);
-                dst = smem_u32(v_s + st * TILE_BYTES);
+                const uint32_t full = BAR(sh.bar.v_full, st), dst = smem_u32(v_s + st * TILE_BYTES);
                 mbar_expect_tx(full, TILE_BYTES);
                 tma_load_4d(dst, &tm_v, full, 0, hk, k0, b);
                 tma_load_4d(dst + HALF_BYTES, &tm_v, full, 64, hk, k0, b);
@@ -183,10 +191,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
                     // A: 16 keys = 32 bytes along the swizzled row, the second 64 keys in the second half.
-                    uint64_t ad = smem_desc_sw128(p_addr + (ks >> 2) * HALF_BYTES + (ks & 3) * 32, 16, 1024);
+                    uint64_t ad = desc_at(smem_desc_sw128(p_addr, 16, 1024), (ks >> 2) * HALF_BYTES + (ks & 3) * 32);
                     // B: V rows are keys (K of this product), 128 bytes of head dimension per row and
                     // half: 64-column atoms HALF_BYTES apart (leading), 8-key groups 1024 bytes apart.
-                    uint64_t bd = smem_desc_sw128(v_addr + ks * 2048, HALF_BYTES, 1024);
+                    uint64_t bd = desc_at(smem_desc_sw128(v_addr, HALF_BYTES, 1024), ks * 2048);
                     umma_f16(tmem + 256, ad, bd, IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(BAR(sh.bar.v_empty, st));
@@ -206,8 +214,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-                    umma_f16(tmem + st * BN, smem_desc_sw128(q_addr + off, 16, 1024),
-                             smem_desc_sw128(k_addr + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
+                    umma_f16(tmem + st * BN, desc_at(smem_desc_sw128(q_addr, 16, 1024), off),
+                             desc_at(smem_desc_sw128(k_addr, 16, 1024), off), IDESC_S, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(BAR(sh.bar.k_empty, st));
                 umma_commit(BAR(sh.bar.s_full, st));
@@ -391,7 +399,11 @@ cudaError_t read_sm100_status(unsigned int *status, bool clear) {
     if (clear && *status) {
         unsigned int zero = 0;
         e = cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(unsigned int));
+        if (e != cudaSuccess) return e;
     }
+    unsigned int bwd = 0;
+    e = read_sm100_bwd_status(&bwd, clear);
+    *status |= bwd;
     return e;
 }
 

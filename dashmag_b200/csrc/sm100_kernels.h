@@ -40,5 +40,6 @@ cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap
 // Reads (and optionally clears) the sticky device word the kernels raise when a bounded wait ran
 // out.  Synchronises with the device.
 cudaError_t read_sm100_status(unsigned int *status, bool clear);
+cudaError_t read_sm100_bwd_status(unsigned int *status, bool clear);
 
 }  // namespace dash

@@ -153,6 +153,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     return d;
 }
 
+// The descriptor of the same tile `bytes` further on (a K step inside the swizzled rows, the
+// next group of rows): only the 14-bit address field moves.
+__device__ __forceinline__ uint64_t desc_at(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
 // Instruction descriptor of kind::f16: f32 accumulator, A and B of `fmt` (0 f16, 1 bf16), each
 // K-major (0) or MN-major (1), an M x N tile.
 __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, int fmt, int a_mn_major, int b_mn_major) {
