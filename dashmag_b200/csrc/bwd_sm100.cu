@@ -18,7 +18,9 @@
 // memory - K-major for the score products and MN-major for the gradient products - through two
 // descriptors over the same 128-byte-swizzled bytes.  Warp roles as in the forward: warp 0 issues
 // TMA loads (and, in dkdv, gathers the step's per-query log-sum-exp, delta and key interval),
-// warp 1 issues the MMAs and owns TMEM, warps 2..5 do the elementwise work, one TMEM lane each.
+// warp 1 issues the MMAs and owns TMEM, warps 2..9 do the elementwise work: two warps per quadrant of
+// TMEM lanes, each thread one row (lane) and half of the step's columns, so that every scheduler
+// has two warps of it to interleave.
 // The score buffers and the P / dS buffers are double, so the products of one step run under the
 // elementwise work of its neighbours.  Every mbarrier wait is bounded (sm100_ptx.cuh).
 #include <cuda.h>
@@ -47,8 +49,13 @@ constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes
 constexpr int STEP_BYTES = STEP * HD * 2;  // 16 KiB
 constexpr int STEP_HALF = STEP_BYTES / 2;  // 64 rows of 128 bytes
 constexpr int PS_BYTES = BIG * STEP * 2;   // 16 KiB: a P^T / dS^T / dS tile, 128 rows of 128 bytes
-constexpr int THREADS = 192;        // dq
-constexpr int THREADS_DKDV = 224;   // dkdv: one more warp gathers the per-query vectors
+constexpr int CG = 2;                      // elementwise warps per TMEM lane quadrant: each takes STEP / CG columns
+constexpr int CW = STEP / CG;              // columns of a step per elementwise thread
+constexpr int EW_WARPS = 4 * CG;           // elementwise warps: warps 2 .. 2 + EW_WARPS - 1
+constexpr int EW_THREADS = 32 * EW_WARPS;
+constexpr int AUX_WARP = 2 + EW_WARPS;     // dkdv: one more warp gathers the per-query vectors
+constexpr int THREADS = 32 * (2 + EW_WARPS);        // dq
+constexpr int THREADS_DKDV = 32 * (3 + EW_WARPS);   // dkdv
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <typename T> struct Pack;
@@ -67,25 +74,27 @@ template <> struct Pack<__half> {
     }
 };
 
-// Row `r` of a [128 x 64] 16-bit tile in the layout of a K-major MMA operand: 128 bytes per row,
-// 16-byte chunks XOR-swizzled by the row.
+// Columns [cg * CW, (cg + 1) * CW) of row `r` of a [128 x 64] 16-bit tile in the layout of a K-major
+// MMA operand: 128 bytes per row, 16-byte chunks XOR-swizzled by the row.
 template <typename T>
-__device__ __forceinline__ void store_row64(uint8_t *tile, int r, const float (&x)[STEP]) {
+__device__ __forceinline__ void store_row_cols(uint8_t *tile, int r, int cg, const float (&x)[CW]) {
     uint8_t *row = tile + r * 128;
 #pragma unroll
-    for (int cc = 0; cc < 8; ++cc) {
-        uint4 v = make_uint4(Pack<T>::two(x[cc * 8 + 0], x[cc * 8 + 1]), Pack<T>::two(x[cc * 8 + 2], x[cc * 8 + 3]),
-                             Pack<T>::two(x[cc * 8 + 4], x[cc * 8 + 5]), Pack<T>::two(x[cc * 8 + 6], x[cc * 8 + 7]));
+    for (int i = 0; i < CW / 8; ++i) {
+        const int cc = cg * (CW / 8) + i;
+        uint4 v = make_uint4(Pack<T>::two(x[i * 8 + 0], x[i * 8 + 1]), Pack<T>::two(x[i * 8 + 2], x[i * 8 + 3]),
+                             Pack<T>::two(x[i * 8 + 4], x[i * 8 + 5]), Pack<T>::two(x[i * 8 + 6], x[i * 8 + 7]));
         *reinterpret_cast<uint4 *>(row + ((cc ^ (r & 7)) << 4)) = v;
     }
 }
 
-// 128 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as one
-// contiguous row of 128 elements.
+// `groups` x 32 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as
+// contiguous elements of the row.
 template <typename T>
-__device__ __forceinline__ void store_acc_row(uint32_t taddr, T *dst, float scale, bool write) {
+__device__ __forceinline__ void store_acc_cols(uint32_t taddr, T *dst, float scale, bool write, int groups) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
+        if (c >= groups) break;
         uint32_t o[32];
         tmem_ld32(taddr + c * 32, o);
         tmem_ld_wait();
@@ -103,11 +112,12 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, T *dst, float scal
     }
 }
 
+// HD / CG zero elements.
 template <typename T>
-__device__ __forceinline__ void store_zero_row(T *dst) {
+__device__ __forceinline__ void store_zero_cols(T *dst) {
     const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int c = 0; c < 16; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+    for (int c = 0; c < 16 / CG; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
 }
 
 // The queries [first, end) that may see some key of [k0, k1): a superset cut from the closed form
@@ -172,6 +182,42 @@ constexpr size_t SMEM_BYTES = 1024 + 2 * BIG_BYTES + 4 * STEP_BYTES + 4 * PS_BYT
 }  // namespace
 
 // =================================================================================================
+// Plan: the key blocks of every batch element ordered by falling work
+// =================================================================================================
+// The sweep of a key block is as long as the range of queries that may see it, which under
+// causality and packing differs by two orders of magnitude between blocks; blocks are scheduled in
+// index order, so the order is worth a tiny kernel: one block counts the steps of each key block
+// and ranks them (ties by index, so the order is a pure function of the inputs).
+constexpr int PLAN_MAX = 2048;
+constexpr int PLAN_THREADS = 1024;
+
+__global__ void __launch_bounds__(PLAN_THREADS) bwd_plan_kernel(const Sm100BwdArgs a, int items) {
+    __shared__ int work[PLAN_MAX];
+    const int nkb = (a.tk + BIG - 1) / BIG;
+    for (int i = threadIdx.x; i < items; i += PLAN_THREADS) {
+        const int kt = i % nkb, k0 = kt * BIG;
+        int first, end;
+        query_range(a.mask, k0, min(k0 + BIG, a.tk), a.tq, a.tk, first, end);
+        work[i] = end > first ? (end - (first / STEP) * STEP + STEP - 1) / STEP : 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < items; i += PLAN_THREADS) {
+        const int w = work[i];
+        int rank = 0;
+        for (int j = 0; j < items; ++j) {
+            const int x = work[j];
+            rank += (x > w) || (x == w && j < i);
+        }
+        a.order[rank] = i;
+    }
+}
+
+size_t bwd_sm100_order_bytes(int b, int tk) {
+    const long long items = (long long)b * ((tk + BIG - 1) / BIG);
+    return (size_t)((items * 4 + 255) & ~255LL);
+}
+
+// =================================================================================================
 // dK, dV
 // =================================================================================================
 template <typename T>
@@ -189,7 +235,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     SharedTail &sh = *reinterpret_cast<SharedTail *>(ds_s + 2 * PS_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    // Key blocks are taken in the order the plan kernel left: the ones most queries see first, so
+    // that the longest sweeps start early and the short ones fill the tail.
+    const int nkb = (a.tk + BIG - 1) / BIG;
+    const int item = a.order ? a.order[blockIdx.y] : (int)blockIdx.y;
+    const int hk = blockIdx.x, b = item / nkb, kt = item - b * nkb;
     const int group = a.hq / a.hkv;
     const int k0 = kt * BIG, k1 = min(k0 + BIG, a.tk);
     auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
@@ -202,8 +252,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             mbar_init(BAR(sh.bar.str_empty[i]), 1);
             mbar_init(BAR(sh.bar.aux_full[i]), 32);
             mbar_init(BAR(sh.bar.sc_full[i]), 1);
-            mbar_init(BAR(sh.bar.sc_empty[i]), 128);
-            mbar_init(BAR(sh.bar.ps_full[i]), 128);
+            mbar_init(BAR(sh.bar.sc_empty[i]), EW_THREADS);
+            mbar_init(BAR(sh.bar.ps_full[i]), EW_THREADS);
             mbar_init(BAR(sh.bar.ps_empty[i]), 1);
         }
         mbar_init(BAR(sh.bar.acc_ready), 1);
@@ -253,7 +303,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 tma_load_4d(gd + STEP_HALF, &tm_do, full, 64, h, q0, b);
             }
         }
-    } else if (warp == 6) {
+    } else if (warp == AUX_WARP) {
         // ---------------- the per-query vectors of each step: log-sum-exp, delta, key interval ----------------
         for (int t = 0; t < steps; ++t) {
             const int st = t & 1, ph = (t >> 1) & 1;
@@ -335,8 +385,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             if (!failed) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
-        // ---------------- elementwise: one key row per thread ----------------
+        // ---------------- elementwise: a key row and CW of the step's columns per thread ----------------
         const int lane_base = 32 * (warp & 3);
+        const int cg = (warp - 2) >> 2, col0 = cg * CW;
         const int r = lane_base + lane;
         const int key = k0 + r;
         const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
@@ -348,11 +399,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 break;
             }
             tc_fence_after_sync();
-            float s[STEP], dp[STEP];
-            tmem_ld32(t_lane + COL_ST + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld32(t_lane + COL_ST + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-            tmem_ld32(t_lane + COL_DPT + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-            tmem_ld32(t_lane + COL_DPT + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+            float s[CW], dp[CW];
+            tmem_ld32(t_lane + COL_ST + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + COL_DPT + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
             tmem_ld_wait();
             tc_fence_before_sync();
             mbar_arrive(BAR(sh.bar.sc_empty[st]));
@@ -363,13 +412,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 // is not seen by before the exponentials, in a pass of its own so that the common,
                 // unmasked step pays nothing for it.
 #pragma unroll
-                for (int c = 0; c < STEP; ++c)
-                    s[c] = (open && key >= aux.lo[c] && key < aux.hi[c]) ? s[c] : -INFINITY;
+                for (int c = 0; c < CW; ++c)
+                    s[c] = (open && key >= aux.lo[col0 + c] && key < aux.hi[col0 + c]) ? s[c] : -INFINITY;
             }
 #pragma unroll
-            for (int c4 = 0; c4 < STEP / 4; ++c4) {
-                const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[c4 * 4]);
-                const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[c4 * 4]);
+            for (int c4 = 0; c4 < CW / 4; ++c4) {
+                const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[col0 + c4 * 4]);
+                const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[col0 + c4 * 4]);
                 const float l2v[4] = {l2.x, l2.y, l2.z, l2.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -380,23 +429,24 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 }
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
-            store_row64<T>(pt_s + st * PS_BYTES, r, s);
-            store_row64<T>(ds_s + st * PS_BYTES, r, dp);
+            store_row_cols<T>(pt_s + st * PS_BYTES, r, cg, s);
+            store_row_cols<T>(ds_s + st * PS_BYTES, r, cg, dp);
             fence_proxy_async_smem();
             mbar_arrive(BAR(sh.bar.ps_full[st]));
         }
-        // ---------------- epilogue ----------------
-        T *dk = static_cast<T *>(a.dk) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD;
-        T *dv = static_cast<T *>(a.dv) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD;
+        // ---------------- epilogue: each thread its HD / CG columns of the row ----------------
+        constexpr int EC = HD / CG;
+        T *dk = static_cast<T *>(a.dk) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD + cg * EC;
+        T *dv = static_cast<T *>(a.dv) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD + cg * EC;
         if (steps == 0 || failed) {
             if (key < a.tk && !failed) {
-                store_zero_row(dk);
-                store_zero_row(dv);
+                store_zero_cols(dk);
+                store_zero_cols(dv);
             }
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             tc_fence_after_sync();
-            store_acc_row<T>(t_lane + COL_DV, dv, 1.f, key < a.tk);
-            store_acc_row<T>(t_lane + COL_DK, dk, a.scale, key < a.tk);
+            store_acc_cols<T>(t_lane + COL_DV + cg * EC, dv, 1.f, key < a.tk, EC / 32);
+            store_acc_cols<T>(t_lane + COL_DK + cg * EC, dk, a.scale, key < a.tk, EC / 32);
             tc_fence_before_sync();
         } else {
             failed = true;
@@ -444,8 +494,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             mbar_init(BAR(sh.bar.str_empty[i]), 1);
             mbar_init(BAR(sh.bar.aux_full[i]), 1);
             mbar_init(BAR(sh.bar.sc_full[i]), 1);
-            mbar_init(BAR(sh.bar.sc_empty[i]), 128);
-            mbar_init(BAR(sh.bar.ps_full[i]), 128);
+            mbar_init(BAR(sh.bar.sc_empty[i]), EW_THREADS);
+            mbar_init(BAR(sh.bar.ps_full[i]), EW_THREADS);
             mbar_init(BAR(sh.bar.ps_empty[i]), 1);
         }
         mbar_init(BAR(sh.bar.acc_ready), 1);
@@ -466,7 +516,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (warp >= 2) {
         row_bounds(a.mask, m0 + r, a.tq, a.tk, lo, hi);
         int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
-        if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
+        if (lane == 0 && sw < 4) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }  // one warp per lane quadrant
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -545,8 +595,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (!failed) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
-        // ---------------- elementwise: one query row per thread ----------------
+        // ---------------- elementwise: a query row and CW of the step's columns per thread ----------------
         const int row = m0 + r;
+        const int cg = (warp - 2) >> 2, col0 = cg * CW;
         const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
         const bool padded = a.mask.kind == 1;
         float l2 = INFINITY, dl = 0.f;
@@ -557,50 +608,46 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             dl = a.delta[at];
         }
         for (int t = 0; t < steps && !failed; ++t) {
-            const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * STEP;
-            uint32_t pb[2] = {0, 0};
+            const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * STEP + col0;
+            uint32_t pb = 0;
             if (padded) {
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int key = c0 + i * 32 + lane;
-                    pb[i] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
-                }
+                const int key = c0 + lane;
+                pb = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.sc_full[st]), ph))) { failed = true; break; }
             tc_fence_after_sync();
-            float s[STEP], dp[STEP];
-            tmem_ld32(t_lane + COL_S + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld32(t_lane + COL_S + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-            tmem_ld32(t_lane + COL_DP + st * STEP, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-            tmem_ld32(t_lane + COL_DP + st * STEP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dp[32]));
+            float s[CW], dp[CW];
+            tmem_ld32(t_lane + COL_S + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + COL_DP + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
             tmem_ld_wait();
             tc_fence_before_sync();
             mbar_arrive(BAR(sh.bar.sc_empty[st]));
 
-            const bool clear = !padded && c0 >= lo && c0 + STEP <= hi;
+            const bool clear = !padded && c0 >= lo && c0 + CW <= hi;
             if (!__all_sync(0xffffffffu, clear)) {
 #pragma unroll
-                for (int c = 0; c < STEP; ++c) {
+                for (int c = 0; c < CW; ++c) {
                     const int key = c0 + c;
-                    s[c] = (key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u)) ? s[c] : -INFINITY;
+                    s[c] = (key >= lo && key < hi && !((pb >> c) & 1u)) ? s[c] : -INFINITY;
                 }
             }
 #pragma unroll
-            for (int c = 0; c < STEP; ++c) {
+            for (int c = 0; c < CW; ++c) {
                 const float p = ex2(fmaf(s[c], a.scale_log2, -l2));
                 dp[c] = p * (dp[c] - dl);
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
-            store_row64<T>(ds_s + st * PS_BYTES, r, dp);
+            store_row_cols<T>(ds_s + st * PS_BYTES, r, cg, dp);
             fence_proxy_async_smem();
             mbar_arrive(BAR(sh.bar.ps_full[st]));
         }
-        T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD;
+        constexpr int EC = HD / CG;
+        T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + cg * EC;
         if (steps == 0 || failed) {
-            if (row < a.tq && !failed) store_zero_row(dq);
+            if (row < a.tq && !failed) store_zero_cols(dq);
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             tc_fence_after_sync();
-            store_acc_row<T>(t_lane + COL_DQ, dq, a.scale, row < a.tq);
+            store_acc_cols<T>(t_lane + COL_DQ + cg * EC, dq, a.scale, row < a.tq, EC / 32);
             tc_fence_before_sync();
         } else {
             failed = true;
@@ -618,16 +665,27 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 // -------------------------------------------------------------------------------------------------
 template <typename T>
-static cudaError_t launch_t(const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream) {
+static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t stream, int *launches) {
     cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return e;
     dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
     bwd_dq_sm100_kernel<T><<<gq, THREADS, SMEM_BYTES, stream>>>(m.q128, m.do128, m.k64, m.v64, a);
+    *launches += 1;
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    dim3 gk((a.tk + BIG - 1) / BIG, a.hkv, a.b);
+    const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);
+    if (a.order && items > 1 && items <= PLAN_MAX) {
+        bwd_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(a, (int)items);
+        *launches += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    } else {
+        a.order = nullptr;  // too many to rank in one block (or nothing to rank): index order
+    }
+    if (items > 65535) return cudaErrorInvalidConfiguration;
+    dim3 gk(a.hkv, (unsigned)items, 1);
     bwd_dkdv_sm100_kernel<T><<<gk, THREADS_DKDV, SMEM_BYTES, stream>>>(m.k128, m.v128, m.q64, m.do64, a);
+    *launches += 1;
     return cudaGetLastError();
 }
 
@@ -641,8 +699,8 @@ cudaError_t read_sm100_bwd_status(unsigned int *status, bool clear) {
     return e;
 }
 
-cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream) {
-    return dtype == DASH_ATTN_BF16 ? launch_t<__nv_bfloat16>(m, a, stream) : launch_t<__half>(m, a, stream);
+cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream, int *launches) {
+    return dtype == DASH_ATTN_BF16 ? launch_t<__nv_bfloat16>(m, a, stream, launches) : launch_t<__half>(m, a, stream, launches);
 }
 
 }  // namespace dash

@@ -96,12 +96,13 @@ bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const 
     if (!q || !k || !v) return false;
     if (!tma_readable(q, p->q_stride) || !tma_readable(k, p->k_stride) || !tma_readable(v, p->v_stride)) return false;
     if (p->hq > 65535 || p->b > 65535) return false;
+    if (backward && (long long)p->b * ((p->tk + 127) / 128) > 65535) return false;  // the dkdv grid's y extent
     if (!device_is_sm100() || !encoder()) return false;
     return true;
 }
 
 size_t sm100_forward_workspace(const dash_attn_params *) { return 0; }
-size_t sm100_backward_workspace(const dash_attn_params *) { return 0; }
+size_t sm100_backward_workspace(const dash_attn_params *p) { return bwd_sm100_order_bytes(p->b, p->tk); }
 
 cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *, cudaStream_t stream, int *launches,
                           std::string &err) {
@@ -124,7 +125,7 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     return e;
 }
 
-cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *, cudaStream_t stream, int *launches,
+cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *workspace, cudaStream_t stream, int *launches,
                            bool *atomic, std::string &err) {
     *atomic = false;  // both kernels sum in a fixed order whatever `deterministic` says
     Sm100BwdMaps m;
@@ -151,9 +152,8 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     f.delta = a.delta;
     f.dq = a.dq; f.dk = a.dk; f.dv = a.dv;
     f.mask = a.mask;
-    e = launch_bwd_sm100(p->dtype, m, f, stream);
-    *launches += 2;
-    return e;
+    f.order = static_cast<int *>(workspace);
+    return launch_bwd_sm100(p->dtype, m, f, stream, launches);
 }
 
 }  // namespace dash

@@ -24,6 +24,7 @@ struct Sm100BwdArgs {
     const float *delta;  // [B,Tq,Hq], rowsum(dO * O)
     void *dq, *dk, *dv;  // contiguous, the inputs' dtype
     MaskArgs mask;
+    int *order;          // scratch: the key blocks in order of falling work, [B * ceil(Tk / 128)]
 };
 
 // Tensor maps of the backward: each tensor once with boxes of 128 rows (the tile a block keeps)
@@ -33,7 +34,9 @@ struct Sm100BwdMaps {
     CUtensorMap k128, v128, q64, do64;   // dkdv kernel
 };
 
-cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream);
+// Adds the kernels it launched to *launches.
+cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream, int *launches);
+size_t bwd_sm100_order_bytes(int b, int tk);
 
 cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                              const Sm100FwdArgs &a, cudaStream_t stream);
