@@ -7,9 +7,10 @@
 //     owns one (chunk, key-value head) and all the query heads of that head's group, so that a
 //     cache row is read once for the whole group; warps of a block take consecutive key-value
 //     heads of the same chunk, so a block streams whole contiguous cache rows;
-//   * D / 8 lanes share a key: each lane loads 16 bytes of the key row and 16 bytes of the value
-//     row (bf16 / f16; two 16-byte loads each for f32) - fully coalesced 128-bit loads - and owns
-//     eight head dimensions of the output; four keys per lane group are in flight at once;
+//   * D / 8 lanes share a key: each lane copies 16 bytes of the key row and 16 bytes of the value
+//     row (bf16 / f16; two 16-byte vectors each for f32) - fully coalesced 128-bit accesses - and
+//     owns eight head dimensions of the output; the copies are asynchronous, into a ring of
+//     shared memory private to the lane, three steps of four keys ahead of the arithmetic;
 //   * scores are reduced across the D / 8 lanes with shuffles, the softmax is kept online in f32
 //     per query head, lane groups are merged with shuffles at the end, and each warp writes one
 //     normalised partial output and its log-sum-exp;
@@ -26,8 +27,9 @@
 
 namespace dash {
 
-constexpr int DEC_WARPS = 8;
-constexpr int DEC_UNROLL = 4;
+constexpr int DEC_WARPS = 4;    // warps per block, each with its own (chunk, key-value head)
+constexpr int DEC_UNROLL = 4;   // keys per group of D / 8 lanes in one step
+constexpr int DEC_STAGES = 4;   // steps of the per-lane ring (16-bit dtypes; two for f32)
 
 template <typename T>
 __device__ __forceinline__ void load8(const T *p, bool valid, float (&x)[8]);
@@ -73,16 +75,68 @@ template <> __device__ __forceinline__ float soft_exp<float>(float x) { return e
 template <typename T> __device__ __forceinline__ float soft_log(float x) { return __logf(x); }
 template <> __device__ __forceinline__ float soft_log<float>(float x) { return logf(x); }
 
+// ---- 16-byte asynchronous copies, global -> this lane's slots of shared memory ------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+    // An invalid (out of range) key copies nothing and fills its slot with zeros.
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Eight values of T from this lane's own 16-byte slots.
+template <typename T>
+__device__ __forceinline__ void slot8(const uint4 *slot, float (&x)[8]);
+template <>
+__device__ __forceinline__ void slot8<float>(const uint4 *slot, float (&x)[8]) {
+    const uint4 a = slot[0], b = slot[32];
+    x[0] = __uint_as_float(a.x); x[1] = __uint_as_float(a.y); x[2] = __uint_as_float(a.z); x[3] = __uint_as_float(a.w);
+    x[4] = __uint_as_float(b.x); x[5] = __uint_as_float(b.y); x[6] = __uint_as_float(b.z); x[7] = __uint_as_float(b.w);
+}
+template <>
+__device__ __forceinline__ void slot8<__nv_bfloat16>(const uint4 *slot, float (&x)[8]) {
+    const uint4 r = slot[0];
+    const unsigned u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[2 * i] = __uint_as_float(u[i] << 16);
+        x[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+}
+template <>
+__device__ __forceinline__ void slot8<__half>(const uint4 *slot, float (&x)[8]) {
+    const uint4 r = slot[0];
+    const unsigned u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[i]));
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+
 // One warp per (chunk, key-value head, pass over GH query heads of the group).
+//
+// The cache rows reach the arithmetic through a ring of shared memory that is private to each
+// lane: a lane copies, with 16-byte asynchronous copies, exactly the bytes it will later read
+// itself, DEC_STAGES - 1 steps ahead (a step is DEC_UNROLL keys for each group of D / 8 lanes).
+// The bytes in flight therefore cost shared memory, not registers, no lane ever waits for
+// another, and a multiprocessor keeps three blocks of four such warps resident: twelve warps
+// with three steps each on the way from HBM.
 template <typename T, int D, int GH>
 __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs a) {
-    constexpr int LPK = D / 8;       // lanes per key
-    constexpr int KPW = 32 / LPK;    // keys per warp step
-    const int lane = threadIdx.x & 31;
+    constexpr int LPK = D / 8;                    // lanes per key
+    constexpr int KPW = 32 / LPK;                 // keys per warp in one load
+    constexpr int VPK = sizeof(T) == 4 ? 2 : 1;   // 16-byte vectors per eight values
+    constexpr int SLOTS = 2 * DEC_UNROLL * VPK;   // this lane's vectors per stage: K and V of DEC_UNROLL keys
+    constexpr int NS = sizeof(T) == 4 ? 2 : DEC_STAGES;
+    extern __shared__ uint4 ring[];               // [warp][stage][slot][lane]
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int group = a.hq / a.hkv;
     const int passes = (group + GH - 1) / GH;
     const int b = blockIdx.y;
-    long long unit = (long long)blockIdx.x * DEC_WARPS + (threadIdx.x >> 5);
+    long long unit = (long long)blockIdx.x * DEC_WARPS + wib;
     const int hk = (int)(unit % a.hkv);
     unit /= a.hkv;
     const int pass = (int)(unit % passes);
@@ -112,46 +166,81 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
     const T *kbase = static_cast<const T *>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)hk * a.k.sh + dl * 8;
     const T *vbase = static_cast<const T *>(a.v.ptr) + (int64_t)b * a.v.sb + (int64_t)hk * a.v.sh + dl * 8;
 
-    for (int base = c0; base < c1; base += KPW * DEC_UNROLL) {
-        float kx[DEC_UNROLL][8], vx[DEC_UNROLL][8];
-        bool valid[DEC_UNROLL];
-#pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u) {
-            const int key = base + u * KPW + sub;
-            valid[u] = key < c1;
-            load8<T>(kbase + (int64_t)key * a.k.st, valid[u], kx[u]);
-            load8<T>(vbase + (int64_t)key * a.v.st, valid[u], vx[u]);
-        }
-#pragma unroll
-        for (int g = 0; g < GH; ++g) {
-            float s[DEC_UNROLL];
-            float mx = -INFINITY;
+    uint4 *mine = ring + (size_t)wib * NS * SLOTS * 32 + lane;
+    const uint32_t mine_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(mine));
+    constexpr int STEP_KEYS = KPW * DEC_UNROLL;
+    const int iters = (c1 - c0 + STEP_KEYS - 1) / STEP_KEYS;
+
+    auto issue = [&](int it) {
+        if (it < iters) {
+            const uint32_t dst = mine_u32 + (uint32_t)((it % NS) * SLOTS * 32 * 16);
 #pragma unroll
             for (int u = 0; u < DEC_UNROLL; ++u) {
+                const int key = c0 + it * STEP_KEYS + u * KPW + sub;
+                const bool valid = key < c1;
+                const T *kp = kbase + (int64_t)(valid ? key : c0) * a.k.st;
+                const T *vp = vbase + (int64_t)(valid ? key : c0) * a.v.st;
+#pragma unroll
+                for (int x = 0; x < VPK; ++x) {
+                    cp_async16(dst + (uint32_t)(((2 * u) * VPK + x) * 32 * 16), reinterpret_cast<const char *>(kp) + 16 * x, valid);
+                    cp_async16(dst + (uint32_t)(((2 * u + 1) * VPK + x) * 32 * 16), reinterpret_cast<const char *>(vp) + 16 * x, valid);
+                }
+            }
+        }
+        cp_async_commit();  // always, so that the group count stays in step with the iterations
+    };
+
+#pragma unroll
+    for (int s = 0; s < NS - 1; ++s) issue(s);
+    for (int it = 0; it < iters; ++it) {
+        issue(it + NS - 1);
+        cp_async_wait<NS - 1>();
+        const uint4 *stage = mine + (size_t)(it % NS) * SLOTS * 32;
+        const int key0 = c0 + it * STEP_KEYS + sub;
+        float s[GH][DEC_UNROLL];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float kx[8];
+            slot8<T>(stage + (2 * u) * VPK * 32, kx);
+            const bool valid = key0 + u * KPW < c1;
+#pragma unroll
+            for (int g = 0; g < GH; ++g) {
                 float d = 0.f;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) d = fmaf(q[g][c], kx[u][c], d);
+                for (int c = 0; c < 8; ++c) d = fmaf(q[g][c], kx[c], d);
 #pragma unroll
                 for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                s[u] = valid[u] ? d * a.scale : -INFINITY;
-                mx = fmaxf(mx, s[u]);
+                s[g][u] = valid ? d * a.scale : -INFINITY;
             }
+        }
+        float corr[GH];
+#pragma unroll
+        for (int g = 0; g < GH; ++g) {
+            float mx = s[g][0];
+#pragma unroll
+            for (int u = 1; u < DEC_UNROLL; ++u) mx = fmaxf(mx, s[g][u]);
             const float mn = fmaxf(m[g], mx);
-            if (mn != -INFINITY) {
-                const float corr = soft_exp<T>(m[g] - mn);
-                float sum = 0.f;
+            const float base = mn == -INFINITY ? 0.f : mn;   // nothing seen yet: exponentiate against 0
+            corr[g] = soft_exp<T>(m[g] - base);
+            float sum = 0.f;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) acc[g][c] *= corr;
-#pragma unroll
-                for (int u = 0; u < DEC_UNROLL; ++u) {
-                    const float p = soft_exp<T>(s[u] - mn);
-                    sum += p;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) acc[g][c] = fmaf(p, vx[u][c], acc[g][c]);
-                }
-                l[g] = l[g] * corr + sum;
-                m[g] = mn;
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                s[g][u] = soft_exp<T>(s[g][u] - base);
+                sum += s[g][u];
             }
+            l[g] = l[g] * corr[g] + sum;
+            m[g] = mn;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[g][c] *= corr[g];
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float vx[8];
+            slot8<T>(stage + (2 * u + 1) * VPK * 32, vx);
+#pragma unroll
+            for (int g = 0; g < GH; ++g)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc[g][c] = fmaf(s[g][u], vx[c], acc[g][c]);
         }
     }
 
@@ -240,9 +329,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_scalar_kernel(Dec
     if (lane == 0) a.part_lse[((int64_t)b * a.hq + h) * a.splits + split] = l > 0.f ? m + logf(l) : -INFINITY;
 }
 
-// Merges the partials of one (sequence, query head) by their log-sum-exp.
+// Merges the partials of one (sequence, query head) by their log-sum-exp: the weights once into
+// shared memory, then every thread its head dimensions over the splits.
+constexpr int MERGE_MAX = 1024;  // splits whose weights fit the shared array; more are folded in passes
+
 template <typename T>
 __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeArgs a) {
+    __shared__ float w[MERGE_MAX];
+    __shared__ float red[4];
     const int bh = blockIdx.x;
     const int b = bh / a.hq;
     int first, len;
@@ -256,16 +350,45 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeArgs a) {
     const float *lse = a.part_lse + (int64_t)bh * a.splits;
     const float *po = a.part_o + (int64_t)bh * a.splits * a.d;
     float mx = -INFINITY;
-    for (int i = 0; i < n; ++i) mx = fmaxf(mx, lse[i]);
-    for (int c = threadIdx.x; c < a.d; c += blockDim.x) {
-        float num = 0.f, den = 0.f;
-        for (int i = 0; i < n; ++i) {
-            const float w = expf(lse[i] - mx);
-            den += w;
-            num = fmaf(w, po[(int64_t)i * a.d + c], num);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, lse[i]);
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+
+    float num[2] = {0.f, 0.f}, den = 0.f;  // a.d <= 256: two head dimensions per thread at most
+    for (int i0 = 0; i0 < n; i0 += MERGE_MAX) {
+        const int m = min(MERGE_MAX, n - i0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < m; i += blockDim.x) w[i] = expf(lse[i0 + i] - mx);
+        __syncthreads();
+#pragma unroll 4
+        for (int i = 0; i < m; ++i) {
+            const float wi = w[i];
+            den += wi;
+            const float *row = po + (int64_t)(i0 + i) * a.d;
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int c = threadIdx.x + 128 * k;
+                if (c < a.d) num[k] = fmaf(wi, row[c], num[k]);
+            }
         }
-        out[c] = Num<T>::from_f32(den > 0.f ? num / den : 0.f);
     }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int c = threadIdx.x + 128 * k;
+        if (c < a.d) out[c] = Num<T>::from_f32(den > 0.f ? num[k] / den : 0.f);
+    }
+}
+
+template <typename T, int D, int GH>
+static cudaError_t split_vec_g(const DecodeArgs &a, dim3 grid, cudaStream_t stream) {
+    constexpr int VPK = sizeof(T) == 4 ? 2 : 1, NS = sizeof(T) == 4 ? 2 : DEC_STAGES;
+    constexpr size_t smem = (size_t)DEC_WARPS * NS * (2 * DEC_UNROLL * VPK) * 32 * 16;
+    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<T, D, GH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    decode_split_kernel<T, D, GH><<<grid, DEC_WARPS * 32, smem, stream>>>(a);
+    return cudaGetLastError();
 }
 
 template <typename T, int D>
@@ -275,10 +398,9 @@ static cudaError_t split_vec(const DecodeArgs &a, cudaStream_t stream) {
     const int passes = (group + gh - 1) / gh;
     const long long units = (long long)a.splits * a.hkv * passes;
     dim3 grid((unsigned)((units + DEC_WARPS - 1) / DEC_WARPS), a.b);
-    if (gh == 4) decode_split_kernel<T, D, 4><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-    else if (gh == 2) decode_split_kernel<T, D, 2><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-    else decode_split_kernel<T, D, 1><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-    return cudaGetLastError();
+    if (gh == 4) return split_vec_g<T, D, 4>(a, grid, stream);
+    if (gh == 2) return split_vec_g<T, D, 2>(a, grid, stream);
+    return split_vec_g<T, D, 1>(a, grid, stream);
 }
 
 template <typename T>
