@@ -336,53 +336,61 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             mbar_arrive(BAR(sh.bar.aux_full[st]));
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0 && steps > 0) {
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+        if (steps > 0) {
             constexpr uint32_t IDESC_SC = idesc_f16(BIG, STEP, Pack<T>::FMT, 0, 0);   // [128 keys x 64 queries]
             constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 keys x 128 d], B MN-major
-            const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s), 16, 1024), v_desc = smem_desc_sw128(smem_u32(v_s), 16, 1024);
             auto grads = [&](int i) -> bool {
                 const int st = i & 1, ph = (i >> 1) & 1;
-                if (!mbar_wait(BAR(sh.bar.ps_full[st]), ph)) return false;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_full[st]), ph))) return false;
                 tc_fence_after_sync();
-                const uint32_t pt = smem_u32(pt_s + st * PS_BYTES), ds = smem_u32(ds_s + st * PS_BYTES);
-                const uint32_t qa = smem_u32(q_s + st * STEP_BYTES), ga = smem_u32(do_s + st * STEP_BYTES);
+                const uint64_t pt = smem_desc_sw128(smem_u32(pt_s + st * PS_BYTES), 16, 1024);
+                const uint64_t ds = smem_desc_sw128(smem_u32(ds_s + st * PS_BYTES), 16, 1024);
+                // The streamed tiles as MN-major B operands: rows are the K of these products.
+                const uint64_t qm = smem_desc_sw128(smem_u32(q_s + st * STEP_BYTES), STEP_HALF, 1024);
+                const uint64_t gm = smem_desc_sw128(smem_u32(do_s + st * STEP_BYTES), STEP_HALF, 1024);
+                const uint32_t e0 = BAR(sh.bar.str_empty[st]), e1 = BAR(sh.bar.ps_empty[st]);
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < STEP / 16; ++ks)   // dV += P^T dO over 64 queries
-                    umma_f16(tmem + COL_DV, desc_at(smem_desc_sw128(pt, 16, 1024), ks * 32),
-                             desc_at(smem_desc_sw128(ga, STEP_HALF, 1024), ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < STEP / 16; ++ks)   // dV += P^T dO over 64 queries
+                        umma_f16(tmem + COL_DV, desc_at(pt, ks * 32), desc_at(gm, ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < STEP / 16; ++ks)   // dK += dS^T Q
-                    umma_f16(tmem + COL_DK, desc_at(smem_desc_sw128(ds, 16, 1024), ks * 32),
-                             desc_at(smem_desc_sw128(qa, STEP_HALF, 1024), ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(BAR(sh.bar.str_empty[st]));
-                umma_commit(BAR(sh.bar.ps_empty[st]));
+                    for (int ks = 0; ks < STEP / 16; ++ks)   // dK += dS^T Q
+                        umma_f16(tmem + COL_DK, desc_at(ds, ks * 32), desc_at(qm, ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(e0);
+                    umma_commit(e1);
+                }
+                __syncwarp();
                 return true;
             };
-            if (!mbar_wait(BAR(sh.bar.res_full), 0)) failed = true;
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.res_full), 0))) failed = true;
             for (int t = 0; t < steps && !failed; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1;
-                if (!mbar_wait(BAR(sh.bar.str_full[st]), ph) || !mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_full[st]), ph) && mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1))) {
                     failed = true;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t qa = smem_u32(q_s + st * STEP_BYTES), ga = smem_u32(do_s + st * STEP_BYTES);
+                const uint64_t qk = smem_desc_sw128(smem_u32(q_s + st * STEP_BYTES), 16, 1024);
+                const uint64_t gk = smem_desc_sw128(smem_u32(do_s + st * STEP_BYTES), 16, 1024);
+                const uint32_t full = BAR(sh.bar.sc_full[st]);
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
-                    umma_f16(tmem + COL_ST + st * STEP,
-                             desc_at(smem_desc_sw128(k_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                             desc_at(smem_desc_sw128(qa, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
+                        umma_f16(tmem + COL_ST + st * STEP, desc_at(k_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(qk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
-                    umma_f16(tmem + COL_DPT + st * STEP,
-                             desc_at(smem_desc_sw128(v_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                             desc_at(smem_desc_sw128(ga, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
-                umma_commit(BAR(sh.bar.sc_full[st]));
+                    for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
+                        umma_f16(tmem + COL_DPT + st * STEP, desc_at(v_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(gk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    umma_commit(full);
+                }
+                __syncwarp();
                 if (t > 0 && !grads(t - 1)) { failed = true; break; }
             }
             if (!failed && !grads(steps - 1)) failed = true;
-            if (!failed) umma_commit(BAR(sh.bar.acc_ready));
+            if (!failed && elect_one()) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
         // ---------------- elementwise: a key row and CW of the step's columns per thread ----------------
@@ -552,47 +560,55 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && steps > 0) {
+        // MMA issuer: the whole warp runs the loop, one elected lane issues.
+        if (steps > 0) {
             constexpr uint32_t IDESC_SC = idesc_f16(BIG, STEP, Pack<T>::FMT, 0, 0);   // [128 queries x 64 keys]
             constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 queries x 128 d]
-            const uint32_t q_addr = smem_u32(q_s), g_addr = smem_u32(do_s);
+            const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s), 16, 1024), g_desc = smem_desc_sw128(smem_u32(do_s), 16, 1024);
             auto grads = [&](int i) -> bool {
                 const int st = i & 1, ph = (i >> 1) & 1;
-                if (!mbar_wait(BAR(sh.bar.ps_full[st]), ph)) return false;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_full[st]), ph))) return false;
                 tc_fence_after_sync();
-                const uint32_t ds = smem_u32(ds_s + st * PS_BYTES), ka = smem_u32(k_s + st * STEP_BYTES);
+                const uint64_t ds = smem_desc_sw128(smem_u32(ds_s + st * PS_BYTES), 16, 1024);
+                const uint64_t km = smem_desc_sw128(smem_u32(k_s + st * STEP_BYTES), STEP_HALF, 1024);
+                const uint32_t e0 = BAR(sh.bar.str_empty[st]), e1 = BAR(sh.bar.ps_empty[st]);
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < STEP / 16; ++ks)   // dQ += dS K over 64 keys
-                    umma_f16(tmem + COL_DQ, desc_at(smem_desc_sw128(ds, 16, 1024), ks * 32),
-                             desc_at(smem_desc_sw128(ka, STEP_HALF, 1024), ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(BAR(sh.bar.str_empty[st]));
-                umma_commit(BAR(sh.bar.ps_empty[st]));
+                    for (int ks = 0; ks < STEP / 16; ++ks)   // dQ += dS K over 64 keys
+                        umma_f16(tmem + COL_DQ, desc_at(ds, ks * 32), desc_at(km, ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(e0);
+                    umma_commit(e1);
+                }
+                __syncwarp();
                 return true;
             };
-            if (!mbar_wait(BAR(sh.bar.res_full), 0)) failed = true;
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.res_full), 0))) failed = true;
             for (int t = 0; t < steps && !failed; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1;
-                if (!mbar_wait(BAR(sh.bar.str_full[st]), ph) || !mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_full[st]), ph) && mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1))) {
                     failed = true;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t ka = smem_u32(k_s + st * STEP_BYTES), va = smem_u32(v_s + st * STEP_BYTES);
+                const uint64_t kk = smem_desc_sw128(smem_u32(k_s + st * STEP_BYTES), 16, 1024);
+                const uint64_t vk = smem_desc_sw128(smem_u32(v_s + st * STEP_BYTES), 16, 1024);
+                const uint32_t full = BAR(sh.bar.sc_full[st]);
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)   // S = Q K^T
-                    umma_f16(tmem + COL_S + st * STEP,
-                             desc_at(smem_desc_sw128(q_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                             desc_at(smem_desc_sw128(ka, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < HD / 16; ++ks)   // S = Q K^T
+                        umma_f16(tmem + COL_S + st * STEP, desc_at(q_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(kk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)   // dP = dO V^T
-                    umma_f16(tmem + COL_DP + st * STEP,
-                             desc_at(smem_desc_sw128(g_addr, 16, 1024), (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                             desc_at(smem_desc_sw128(va, 16, 1024), (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
-                umma_commit(BAR(sh.bar.sc_full[st]));
+                    for (int ks = 0; ks < HD / 16; ++ks)   // dP = dO V^T
+                        umma_f16(tmem + COL_DP + st * STEP, desc_at(g_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(vk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    umma_commit(full);
+                }
+                __syncwarp();
                 if (t > 0 && !grads(t - 1)) { failed = true; break; }
             }
             if (!failed && !grads(steps - 1)) failed = true;
-            if (!failed) umma_commit(BAR(sh.bar.acc_ready));
+            if (!failed && elect_one()) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
         // ---------------- elementwise: a query row and CW of the step's columns per thread ----------------

@@ -177,48 +177,54 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0 && n_tiles > 0) {
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+        if (n_tiles > 0) {
             constexpr uint32_t IDESC_S = idesc_f16(BM, BN, Pack<T>::FMT, 0, 0);   // A = Q, B = K, both K-major
             constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // A = P K-major, B = V MN-major
-            const uint32_t q_addr = smem_u32(q_s);
+            const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s), 16, 1024);
             auto issue_pv = [&](int i) -> bool {
                 const int st = i & 1, ph = (i >> 1) & 1;
-                if (!mbar_wait(BAR(sh.bar.v_full, st), ph)) return false;
-                if (!mbar_wait(BAR(sh.bar.p_full, st), ph)) return false;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full, st), ph) && mbar_wait(BAR(sh.bar.p_full, st), ph)))
+                    return false;
                 tc_fence_after_sync();
-                const uint32_t p_addr = smem_u32(p_s + st * TILE_BYTES), v_addr = smem_u32(v_s + st * TILE_BYTES);
+                // A = P: 16 keys = 32 bytes along the swizzled row, the second 64 keys in the second half.
+                // B = V: rows are keys (K of this product), 128 bytes of head dimension per row and half:
+                // 64-column atoms HALF_BYTES apart (leading), 8-key groups 1024 bytes apart.
+                const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s + st * TILE_BYTES), 16, 1024);
+                const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * TILE_BYTES), HALF_BYTES, 1024);
+                const uint32_t v_empty = BAR(sh.bar.v_empty, st), p_empty = BAR(sh.bar.p_empty, st);
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    // A: 16 keys = 32 bytes along the swizzled row, the second 64 keys in the second half.
-                    uint64_t ad = desc_at(smem_desc_sw128(p_addr, 16, 1024), (ks >> 2) * HALF_BYTES + (ks & 3) * 32);
-                    // B: V rows are keys (K of this product), 128 bytes of head dimension per row and
-                    // half: 64-column atoms HALF_BYTES apart (leading), 8-key groups 1024 bytes apart.
-                    uint64_t bd = desc_at(smem_desc_sw128(v_addr, HALF_BYTES, 1024), ks * 2048);
-                    umma_f16(tmem + 256, ad, bd, IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < BN / 16; ++ks)
+                        umma_f16(tmem + 256, desc_at(p_desc, (ks >> 2) * HALF_BYTES + (ks & 3) * 32), desc_at(v_desc, ks * 2048),
+                                 IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(v_empty);
+                    umma_commit(p_empty);
+                    umma_commit(o_ready);
                 }
-                umma_commit(BAR(sh.bar.v_empty, st));
-                umma_commit(BAR(sh.bar.p_empty, st));
-                umma_commit(o_ready);
+                __syncwarp();
                 return true;
             };
-            if (!mbar_wait(q_full, 0)) failed = true;
+            if (!__all_sync(0xffffffffu, mbar_wait(q_full, 0))) failed = true;
             for (int j = 0; j < n_tiles && !failed; ++j) {
                 const int st = j & 1, ph = (j >> 1) & 1;
-                if (!mbar_wait(BAR(sh.bar.k_full, st), ph) || !mbar_wait(BAR(sh.bar.s_empty, st), ph ^ 1)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full, st), ph) && mbar_wait(BAR(sh.bar.s_empty, st), ph ^ 1))) {
                     failed = true;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t k_addr = smem_u32(k_s + st * TILE_BYTES);
+                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + st * TILE_BYTES), 16, 1024);
+                const uint32_t k_empty = BAR(sh.bar.k_empty, st), s_full = BAR(sh.bar.s_full, st);
+                if (elect_one()) {
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-                    umma_f16(tmem + st * BN, desc_at(smem_desc_sw128(q_addr, 16, 1024), off),
-                             desc_at(smem_desc_sw128(k_addr, 16, 1024), off), IDESC_S, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < HD / 16; ++ks) {
+                        const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+                        umma_f16(tmem + st * BN, desc_at(q_desc, off), desc_at(k_desc, off), IDESC_S, ks > 0 ? 1u : 0u);
+                    }
+                    umma_commit(k_empty);
+                    umma_commit(s_full);
                 }
-                umma_commit(BAR(sh.bar.k_empty, st));
-                umma_commit(BAR(sh.bar.s_full, st));
+                __syncwarp();
                 if (j > 0 && !issue_pv(j - 1)) { failed = true; break; }
             }
             if (!failed && !issue_pv(n_tiles - 1)) failed = true;

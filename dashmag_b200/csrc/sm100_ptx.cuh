@@ -56,6 +56,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
 }
 
+// One lane of the (converged) warp, the same one every time it is asked.  The MMA-issuing warp
+// runs its whole loop with all 32 lanes, so that addresses and descriptors are computed in
+// warp-uniform code, and only the issue itself sits under this predicate.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---- proxies and thread sync ---------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
