@@ -151,6 +151,8 @@ __device__ __forceinline__ void query_range(const MaskArgs &m, int k0, int k1, i
     if (end < first) end = first;
 }
 
+constexpr int CU_CACHE = 768;   // offsets of packed sequences kept in shared memory (dkdv)
+
 struct PipeBarriers {
     uint64_t res_full;               // the resident tiles have landed
     uint64_t str_full[2], str_empty[2];  // streamed tiles
@@ -173,11 +175,12 @@ struct SharedTail {
     uint32_t tmem_base;
     unsigned int abort;
     int red_lo[4], red_hi[4];
+    int cu_q[CU_CACHE], cu_k[CU_CACHE];   // dkdv: the packed sequences' offsets, when they fit
 };
 
 // shared memory: 1 KiB slack | resident A, resident B (2 x 32 KiB) | stream ring 2 x (16 + 16 KiB) |
 // P/dS ring 2 x (16 + 16 KiB) | tail
-constexpr size_t SMEM_BYTES = 1024 + 2 * BIG_BYTES + 4 * STEP_BYTES + 4 * PS_BYTES + 4096;
+constexpr size_t SMEM_BYTES = 1024 + 2 * BIG_BYTES + 4 * STEP_BYTES + 4 * PS_BYTES + 10240;
 
 }  // namespace
 
@@ -269,6 +272,19 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     }
     int qfirst, qend;
     query_range(a.mask, k0, k1, a.tq, a.tk, qfirst, qend);
+    // The per-query vectors of every step need each query's key interval, a binary search over the
+    // sequences' offsets: from shared memory when they fit, so that it costs tens of cycles a probe
+    // instead of a trip to L2.
+    MaskArgs qmask = a.mask;
+    if (a.mask.kind == 2 && a.mask.seqs + 1 <= CU_CACHE) {
+        for (int i = threadIdx.x; i <= a.mask.seqs; i += blockDim.x) {
+            sh.cu_q[i] = load_index(a.mask.cu_q, a.mask.idx_bytes, i);
+            sh.cu_k[i] = load_index(a.mask.cu_k, a.mask.idx_bytes, i);
+        }
+        qmask.cu_q = sh.cu_q;
+        qmask.cu_k = sh.cu_k;
+        qmask.idx_bytes = 4;
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -308,27 +324,35 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         for (int t = 0; t < steps; ++t) {
             const int st = t & 1, ph = (t >> 1) & 1;
             const int h = hk * group + t / tiles, q0 = q_begin + (t % tiles) * STEP;
-            // aux[st] is free when the stage is: the elementwise threads of step t - 2 are done with it.
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1))) { failed = true; break; }
-            StepAux &aux = sh.aux[st];
+            // Gather first (loads and the interval search depend on the step alone), wait after: the
+            // latency of the gathering hides behind the wait for the stage.
+            float l2v[2], dlv[2];
+            int lov[2], hiv[2];
             bool clear = true;
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int c = lane + 32 * i, q = q0 + c;
-                int lo, hi;
-                row_bounds(a.mask, q, a.tq, a.tk, lo, hi);
-                float l2 = INFINITY, dl = 0.f;
+                const int q = q0 + lane + 32 * i;
+                l2v[i] = INFINITY;
+                dlv[i] = 0.f;
                 if (q < a.tq) {
                     const int64_t at = ((int64_t)b * a.tq + q) * a.hq + h;
                     const float x = a.lse[at];
-                    l2 = x == -INFINITY ? INFINITY : x * LOG2E;
-                    dl = a.delta[at];
+                    l2v[i] = x == -INFINITY ? INFINITY : x * LOG2E;
+                    dlv[i] = a.delta[at];
                 }
-                aux.lse2[c] = l2;
-                aux.delta[c] = dl;
-                aux.lo[c] = lo;
-                aux.hi[c] = hi;
-                clear = clear && lo <= k0 && hi >= k0 + BIG;
+                row_bounds(qmask, q, a.tq, a.tk, lov[i], hiv[i]);
+                clear = clear && lov[i] <= k0 && hiv[i] >= k0 + BIG;
+            }
+            // aux[st] is free when the stage is: the elementwise threads of step t - 2 are done with it.
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1))) { failed = true; break; }
+            StepAux &aux = sh.aux[st];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c = lane + 32 * i;
+                aux.lse2[c] = l2v[i];
+                aux.delta[c] = dlv[i];
+                aux.lo[c] = lov[i];
+                aux.hi[c] = hiv[i];
             }
             clear = __all_sync(0xffffffffu, clear) && a.mask.kind != 1;
             if (lane == 0) aux.clear = clear ? 1 : 0;
