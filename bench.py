@@ -256,15 +256,33 @@ def main():
         o, lse = A.attention_with_lse(q, k, v, mask, options)
         return (o, lse) + tuple(A.attention_backward(q, k, v, o, lse, g, mask, options))
 
-    def train_step_e2e():
-        dq_, dk_, dv_, dg_ = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "do"))
-        o, lse = A.attention_with_lse(dq_, dk_, dv_, mask, options)
-        gq, gk, gv = A.attention_backward(dq_, dk_, dv_, o, lse, dg_, mask, options)
-        host_out["o"].copy_(o, non_blocking=True)
-        host_lse.copy_(lse, non_blocking=True)
-        host_out["dq"].copy_(gq, non_blocking=True)
-        host_out["dk"].copy_(gk, non_blocking=True)
-        host_out["dv"].copy_(gv, non_blocking=True)
+    # End to end: every step copies its inputs from pinned host memory and its results back.  The
+    # three legs run on three streams over two sets of device input buffers, so that the copy-in of
+    # step i + 1 and the copy-out of step i - 1 overlap the kernels of step i (PCIe is full duplex).
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dev_in = [{n: torch.empty_like(host[n], device=dev) for n in ("q", "k", "v", "do")} for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+
+    def train_step_e2e(i):
+        cur = torch.cuda.current_stream(dev)
+        buf = dev_in[i % 2]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[i % 2])          # the kernels of step i - 2 have read this set
+            for n in ("q", "k", "v", "do"):
+                buf[n].copy_(host[n], non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(s_in)
+        cur.wait_event(ready)
+        o, lse = A.attention_with_lse(buf["q"], buf["k"], buf["v"], mask, options)
+        gq, gk, gv = A.attention_backward(buf["q"], buf["k"], buf["v"], o, lse, buf["do"], mask, options)
+        in_free[i % 2].record(cur)
+        done = torch.cuda.Event()
+        done.record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            for dst, src in ((host_out["o"], o), (host_lse, lse), (host_out["dq"], gq), (host_out["dk"], gk), (host_out["dv"], gv)):
+                dst.copy_(src, non_blocking=True)
+                src.record_stream(s_out)
 
     for _ in range(args.warmup):
         train_step()
@@ -294,19 +312,21 @@ def main():
     value = total_flops / (step_ms * 1e-3) / 1e12
 
     # end to end: host buffers in, results back to the host, every step
-    for _ in range(min(args.warmup, 2)):
-        train_step_e2e()
+    for i in range(2):
+        train_step_e2e(i)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        train_step_e2e()
+    for i in range(args.steps):
+        train_step_e2e(i)
+    torch.cuda.current_stream(dev).wait_stream(s_out)
+    torch.cuda.current_stream(dev).wait_stream(s_in)
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     h2d = sum(host[n].numel() * 2 for n in ("q", "k", "v", "do"))
     d2h = sum(t.numel() * 2 for t in host_out.values()) + host_lse.numel() * 4
-    del host_out
+    del host_out, dev_in
 
     # ---- decoding leg ----
     decode = None
@@ -357,7 +377,9 @@ def main():
                     "h2d_bytes_per_step": qd_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
                          "frac": gbs / world / pk["hbm"], "frac_of_nominal_8TBs": gbs / world / 8000.0,
-                         "traffic": None, "kernels": "decode_split_kernel + decode_merge_kernel (pass-level)"},
+                         # ncu at batch 8 read 1.0154 x the algorithmic bytes; traffic grows with the cache read
+                         "traffic": dec_bytes * 1.0154, "traffic_unit": "bytes per pass (scaled from the batch-8 capture)",
+                         "kernels": "decode_split_kernel + decode_merge_kernel (pass-level)"},
         }
         del kc, vc
 
@@ -378,11 +400,15 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": fwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": fwd_tf / tensor_peak, "frac_of_nominal_2250": fwd_tf / 2250.0,
-                         "peak_source": pk["source"] + " burst (kernel timed alone)", "traffic": None,
-                         "kernel": "forward (1 launch per pass)"},
+                         "peak_source": pk["source"] + " burst (kernel timed alone)",
+                         # dram read + write of one launch, ncu capture of this workload (profiles/fwd_sm100_config2.md)
+                         "traffic": 303.9e6, "traffic_unit": "bytes per launch",
+                         "kernel": "fwd_sm100_kernel (1 launch per pass)"},
             "roofline_backward": {"bound": "tensor", "achieved": bwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                                   "frac": bwd_tf / tensor_peak, "frac_of_nominal_2250": bwd_tf / 2250.0,
-                                  "kernel": "backward pass (delta + gradient kernels)"},
+                                  # delta 0.26 GB + dq 0.45 GB + dkdv 0.99 GB (profiles/bwd_*_config2.md)
+                                  "traffic": 1.70e9, "traffic_unit": "bytes per pass",
+                                  "kernel": "backward pass: generic_delta + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
             "decode": decode,
             "cpu_baseline": None if args.skip_cpu else cpu_baseline(),
         }
