@@ -123,6 +123,15 @@ def cpu_sample_inputs(seed=0):
     return (q, k, v, g), flops, f"1 sequence of {t} tokens, {hq} query / {hkv} kv heads, D {d}, causal, fwd+bwd, f32"
 
 
+def cpu_threads():
+    """Every host core this process may run on: launchers such as torch.distributed.run set
+    OMP_NUM_THREADS=1, which would time the CPU arm on one thread."""
+    from oracle import attention_oracle as oracle
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.set_threads(n)
+    return oracle.threads()
+
+
 def cpu_step(inputs):
     from oracle import attention_oracle as oracle
     q, k, v, g = inputs
@@ -133,6 +142,7 @@ def cpu_step(inputs):
 def cpu_baseline(reps=2):
     from oracle import attention_oracle as oracle
     inputs, flops, sample = cpu_sample_inputs()
+    cpu_threads()
     cpu_step(inputs)
     times = []
     for _ in range(reps):
@@ -149,6 +159,7 @@ def run_reference(args, rank):
         return
     from oracle import attention_oracle as oracle
     inputs, flops, sample = cpu_sample_inputs()
+    cpu_threads()
     for _ in range(args.warmup):
         cpu_step(inputs)
     t0 = time.perf_counter()
