@@ -1,0 +1,431 @@
+// The training forward on the 5th-generation tensor cores, two query tiles per block: bf16 / f16,
+// head dimension 128.
+//
+// A block owns TWO tiles of 128 queries that sweep the same keys - two query heads of one
+// key-value group over the same rows (grouped heads, even group size), or two consecutive row
+// tiles of one head - so that every K / V tile fetched from L2 feeds twice the arithmetic, and it
+// runs two softmax warpgroups, one per tile, so that every scheduler has two warps of elementwise
+// work to interleave.  352 threads:
+//   warp 0, 10  one lane each issues the TMA tile loads: warp 0 both Q tiles once and then the K
+//               tiles of 64 keys, warp 10 the V tiles, into three-stage rings of 128-byte-swizzled
+//               shared memory;
+//   warp 1      owns tensor memory (512 columns: per tile two S buffers of 64 columns and the
+//               128-column O accumulator) and issues the tcgen05 MMAs from warp-uniform code under
+//               an elected lane: S_t = Q_t K_j^T for both tiles, then O_t += P_t V_j of the step
+//               before;
+//   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one query row per thread (TMEM lane =
+//               row): read S from tensor memory, mask what the row does not see, keep the online
+//               softmax in f32 with the scale folded into an exp2, write P rounded to the input
+//               dtype into shared memory in the layout of an MMA A operand, and at the end
+//               normalise O and store it with the row's log-sum-exp.
+// S and P are double per tile, so the products of one step run under the softmax of its neighbours
+// and of the other tile.  Lazy row maximum, masking, bounded waits and the status word as in the
+// one-tile kernel (fwd_sm100.cu), which stays for head dimensions and shapes this one leaves.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.h"
+#include "sm100_kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace dash {
+
+using namespace ptx;
+
+__device__ unsigned int g_sm100_fwd2_status = 0;  // sticky: non-zero once a bounded wait has run out
+
+namespace {
+
+constexpr int BM = 128;                   // queries per tile
+constexpr int BN = 64;                    // keys per step
+constexpr int HD = 128;
+constexpr int NT = 2;                     // query tiles per block
+constexpr int NS = 3;                     // stages of the K and of the V ring
+constexpr int Q_BYTES = BM * HD * 2;      // 32 KiB per tile
+constexpr int Q_HALF = Q_BYTES / 2;       // 128 rows of 128 bytes
+constexpr int KV_BYTES = BN * HD * 2;     // 16 KiB
+constexpr int KV_HALF = KV_BYTES / 2;     // 64 rows of 128 bytes
+constexpr int P_BYTES = BM * BN * 2;      // 16 KiB: 128 rows of 128 bytes
+constexpr int THREADS = 352;
+constexpr int V_WARP = 10;
+constexpr float RESCALE_LOG2 = 8.0f;
+
+struct Barriers {
+    uint64_t q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
+    uint64_t s_full[NT][2], s_empty[NT][2], p_full[NT][2], p_empty[NT][2], o_ready[NT];
+};
+
+struct Shared {
+    Barriers bar;
+    uint32_t tmem_base;
+    int red_lo[4 * NT], red_hi[4 * NT];
+    unsigned int abort;
+};
+
+// 1 KiB slack | Q x 2 | K ring | V ring | P [tile][buffer] | Shared
+constexpr size_t SMEM_BYTES = 1024 + NT * Q_BYTES + 2 * NS * KV_BYTES + NT * 2 * P_BYTES + 1024;
+
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+    static constexpr int FMT = 1;
+    static __device__ __forceinline__ uint32_t two(float a, float b) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+template <> struct Pack<__half> {
+    static constexpr int FMT = 0;
+    static __device__ __forceinline__ uint32_t two(float a, float b) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+
+}  // namespace
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const Sm100FwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *q_s = smem;                       // [NT][Q_BYTES]
+    uint8_t *k_s = q_s + NT * Q_BYTES;         // [NS][KV_BYTES]
+    uint8_t *v_s = k_s + NS * KV_BYTES;        // [NS][KV_BYTES]
+    uint8_t *p_s = v_s + NS * KV_BYTES;        // [NT][2][P_BYTES]
+    Shared &sh = *reinterpret_cast<Shared *>(p_s + NT * 2 * P_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = gridDim.y - 1 - blockIdx.y;  // later (longer, under causality) tiles first
+    const int b = blockIdx.z;
+    // Tile t of the block: head h0 + t over rows m0 (paired heads), or head h0 over rows m0 + 128 t.
+    const int pair = a.pair_heads;
+    const int h0 = pair ? 2 * blockIdx.x : blockIdx.x;
+    const int hk = h0 / (a.hq / a.hkv);
+    const int m_base = pair ? qt * BM : qt * NT * BM;
+    auto tile_head = [&](int t) { return pair ? h0 + t : h0; };
+    auto tile_row0 = [&](int t) { return pair ? m_base : m_base + t * BM; };
+    auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
+
+    if (threadIdx.x == 0) {
+        sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_fwd2_status);
+        mbar_init(BAR(sh.bar.q_full), 1);
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(BAR(sh.bar.k_full[i]), 1);
+            mbar_init(BAR(sh.bar.k_empty[i]), 1);
+            mbar_init(BAR(sh.bar.v_full[i]), 1);
+            mbar_init(BAR(sh.bar.v_empty[i]), 1);
+        }
+        for (int t = 0; t < NT; ++t) {
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(BAR(sh.bar.s_full[t][i]), 1);
+                mbar_init(BAR(sh.bar.s_empty[t][i]), 128);
+                mbar_init(BAR(sh.bar.p_full[t][i]), 128);
+                mbar_init(BAR(sh.bar.p_empty[t][i]), 1);
+            }
+            mbar_init(BAR(sh.bar.o_ready[t]), 1);
+        }
+        fence_mbar_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&sh.tmem_base), 512);
+        tmem_relinquish();
+    }
+
+    // Each softmax thread owns one query row of one tile; the block sweeps the union of all rows'
+    // key intervals.
+    const int sw = warp - 2;                       // 0..7 for softmax warps
+    const int tile = (sw >> 2) & 1;                // which of the two tiles
+    const int lane_base = 32 * (warp & 3);         // the TMEM lanes this warp may touch
+    const int r = lane_base + lane;                // row of the tile
+    int lo = a.tk, hi = 0;
+    if (warp >= 2 && warp < 2 + 4 * NT) {
+        row_bounds(a.mask, tile_row0(tile) + r, a.tq, a.tk, lo, hi);
+        int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
+        if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh.tmem_base;
+    int kmin = a.tk, kmax = 0;
+#pragma unroll
+    for (int i = 0; i < 4 * NT; ++i) { kmin = min(kmin, sh.red_lo[i]); kmax = max(kmax, sh.red_hi[i]); }
+    const bool aborted = sh.abort != 0;
+    const int steps = (!aborted && kmax > kmin) ? (kmax - kmin + BN - 1) / BN : 0;
+    bool failed = aborted;
+    // TMEM columns: S[tile][buffer] at (2 tile + buffer) * 64, O[tile] at 256 + 128 tile.
+    auto COL_S = [](int t, int buf) { return static_cast<uint32_t>((2 * t + buf) * BN); };
+    auto COL_O = [](int t) { return static_cast<uint32_t>(256 + t * HD); };
+
+    if (warp == 0) {
+        // ---------------- TMA producer: both Q tiles, then the K ring ----------------
+        if (lane == 0 && steps > 0) {
+            const uint32_t qf = BAR(sh.bar.q_full);
+            mbar_expect_tx(qf, NT * Q_BYTES);
+            for (int t = 0; t < NT; ++t) {
+                const uint32_t dst = smem_u32(q_s + t * Q_BYTES);
+                tma_load_4d(dst, &tm_q, qf, 0, tile_head(t), tile_row0(t), b);
+                tma_load_4d(dst + Q_HALF, &tm_q, qf, 64, tile_head(t), tile_row0(t), b);
+            }
+            for (int j = 0; j < steps; ++j) {
+                const int st = j % NS, ph = (j / NS) & 1, k0 = kmin + j * BN;
+                if (!mbar_wait(BAR(sh.bar.k_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t full = BAR(sh.bar.k_full[st]), dst = smem_u32(k_s + st * KV_BYTES);
+                mbar_expect_tx(full, KV_BYTES);
+                tma_load_4d(dst, &tm_k, full, 0, hk, k0, b);
+                tma_load_4d(dst + KV_HALF, &tm_k, full, 64, hk, k0, b);
+            }
+        }
+    } else if (warp == V_WARP) {
+        // ---------------- TMA producer of the V ring ----------------
+        if (lane == 0 && steps > 0) {
+            for (int j = 0; j < steps; ++j) {
+                const int st = j % NS, ph = (j / NS) & 1, k0 = kmin + j * BN;
+                if (!mbar_wait(BAR(sh.bar.v_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t full = BAR(sh.bar.v_full[st]), dst = smem_u32(v_s + st * KV_BYTES);
+                mbar_expect_tx(full, KV_BYTES);
+                tma_load_4d(dst, &tm_v, full, 0, hk, k0, b);
+                tma_load_4d(dst + KV_HALF, &tm_v, full, 64, hk, k0, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+        if (steps > 0) {
+            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, Pack<T>::FMT, 0, 0);   // [128 q x 64 keys], A = Q, B = K K-major
+            constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // [128 q x 128 d], A = P, B = V MN-major
+            uint64_t q_desc[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) q_desc[t] = smem_desc_sw128(smem_u32(q_s + t * Q_BYTES), 16, 1024);
+            // O_t += P_t V of step i, for both tiles; V's stage is released after the second.
+            auto issue_pv = [&](int i) -> bool {
+                const int st = i % NS, vph = (i / NS) & 1, pb = i & 1, pph = (i >> 1) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full[st]), vph))) return false;
+                // V rows are keys (the K of this product): 64-column halves KV_HALF apart, 8-key groups 1024 B apart.
+                const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * KV_BYTES), KV_HALF, 1024);
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[t][pb]), pph))) return false;
+                    tc_fence_after_sync();
+                    const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s + (t * 2 + pb) * P_BYTES), 16, 1024);
+                    const uint32_t pe = BAR(sh.bar.p_empty[t][pb]), orr = BAR(sh.bar.o_ready[t]), ve = BAR(sh.bar.v_empty[st]);
+                    if (elect_one()) {
+#pragma unroll
+                        for (int ks = 0; ks < BN / 16; ++ks)
+                            umma_f16(tmem + COL_O(t), desc_at(p_desc, ks * 32), desc_at(v_desc, ks * 2048), IDESC_O,
+                                     (i > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(pe);
+                        umma_commit(orr);
+                        if (t == NT - 1) umma_commit(ve);
+                    }
+                    __syncwarp();
+                }
+                return true;
+            };
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_full), 0))) failed = true;
+            for (int j = 0; j < steps && !failed; ++j) {
+                const int st = j % NS, kph = (j / NS) & 1, sb = j & 1, sph = (j >> 1) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[st]), kph))) { failed = true; break; }
+                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + st * KV_BYTES), 16, 1024);
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_empty[t][sb]), sph ^ 1))) { failed = true; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sf = BAR(sh.bar.s_full[t][sb]), ke = BAR(sh.bar.k_empty[st]);
+                    if (elect_one()) {
+#pragma unroll
+                        for (int ks = 0; ks < HD / 16; ++ks)
+                            umma_f16(tmem + COL_S(t, sb), desc_at(q_desc[t], (ks >> 2) * Q_HALF + (ks & 3) * 32),
+                                     desc_at(k_desc, (ks >> 2) * KV_HALF + (ks & 3) * 32), IDESC_S, ks > 0 ? 1u : 0u);
+                        umma_commit(sf);
+                        if (t == NT - 1) umma_commit(ke);
+                    }
+                    __syncwarp();
+                }
+                if (failed) break;
+                if (j > 0 && !issue_pv(j - 1)) { failed = true; break; }
+            }
+            if (!failed && !issue_pv(steps - 1)) failed = true;
+        }
+    } else {
+        // ---------------- softmax of one tile, one row per thread ----------------
+        const int t = tile, h = tile_head(t);
+        const int row = tile_row0(t) + r;
+        const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
+        const bool padded = a.mask.kind == 1;
+        const float2 sl2 = make_float2(a.scale_log2, a.scale_log2);
+        float m_ref = -INFINITY, l = 0.f;
+        for (int j = 0; j < steps && !failed; ++j) {
+            const int sb = j & 1, sph = (j >> 1) & 1, k0 = kmin + j * BN;
+            uint32_t pb[2] = {0, 0};
+            if (padded) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int key = k0 + i * 32 + lane;
+                    pb[i] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
+                }
+            }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full[t][sb]), sph))) { failed = true; break; }
+            tc_fence_after_sync();
+            float s[BN];
+            tmem_ld32(t_lane + COL_S(t, sb), *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+            tmem_ld32(t_lane + COL_S(t, sb) + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            mbar_arrive(BAR(sh.bar.s_empty[t][sb]));
+
+            const bool clear = !padded && k0 >= lo && k0 + BN <= hi;  // the row sees the whole step
+            if (!__all_sync(0xffffffffu, clear)) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int key = k0 + c;
+                    const bool vis = key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u);
+                    s[c] = vis ? s[c] : -INFINITY;
+                }
+            }
+            // Row maximum: eight independent chains of three-input maxima, then a tree.
+            float mx8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) mx8[e] = fmax3(s[e], s[8 + e], s[16 + e]);
+#pragma unroll
+            for (int c = 24; c < BN; c += 16)
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    mx8[e] = c + 8 + e < BN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
+            const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+            // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8.
+            float factor = 1.f;
+            bool rescale = false;
+            if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated yet for this row (or exact zeros)
+            } else if ((mx - m_ref) * a.scale_log2 > RESCALE_LOG2) {
+                factor = ex2((m_ref - mx) * a.scale_log2);
+                l *= factor;
+                m_ref = mx;
+                rescale = true;
+            }
+            const float neg = m_ref == -INFINITY ? 0.f : -m_ref * a.scale_log2;
+            const float2 neg2 = make_float2(neg, neg);
+
+            // The P buffer is free once P V of step j - 2 has completed.
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_empty[t][sb]), sph ^ 1))) { failed = true; break; }
+            uint8_t *p_row = p_s + (t * 2 + sb) * P_BYTES + r * 128;
+            float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int cc = 0; cc < BN / 8; ++cc) {
+                float p[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 x = fma2(make_float2(s[cc * 8 + 2 * e], s[cc * 8 + 2 * e + 1]), sl2, neg2);
+                    p[2 * e] = ex2(x.x);
+                    p[2 * e + 1] = ex2(x.y);
+                    sum2[e] = add2(sum2[e], make_float2(p[2 * e], p[2 * e + 1]));
+                }
+                uint4 v = make_uint4(Pack<T>::two(p[0], p[1]), Pack<T>::two(p[2], p[3]), Pack<T>::two(p[4], p[5]),
+                                     Pack<T>::two(p[6], p[7]));
+                // 16-byte chunk cc of the row's 128 bytes, XOR-swizzled by the row.
+                *reinterpret_cast<uint4 *>(p_row + ((cc ^ (r & 7)) << 4)) = v;
+            }
+            {
+                const float2 tsum = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+                l += tsum.x + tsum.y;
+            }
+            // O holds steps 0..j-1 once P V of step j - 1 has completed; rescale it before P V of step j.
+            if (j > 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (j - 1) & 1))) { failed = true; break; }
+                if (__any_sync(0xffffffffu, rescale)) {
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(t_lane + COL_O(t) + c * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+                        tmem_st32(t_lane + COL_O(t) + c * 32, o);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(BAR(sh.bar.p_full[t][sb]));
+        }
+
+        // ---------------- epilogue ----------------
+        T *out = static_cast<T *>(a.out);
+        const int64_t base = ((int64_t)b * a.tq + row) * a.hq + h;
+        if (steps == 0 || failed) {
+            if (row < a.tq && !failed) {
+                const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
+                a.lse[base] = -INFINITY;
+            }
+        } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (steps - 1) & 1))) {
+            tc_fence_after_sync();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_lane + COL_O(t) + c * 32, o);
+                tmem_ld_wait();
+                if (row < a.tq) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
+                        v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
+                        v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
+                        v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
+                        reinterpret_cast<uint4 *>(out + base * HD)[c * 4 + e] = v;
+                    }
+                }
+            }
+            if (row < a.tq) a.lse[base] = l > 0.f ? m_ref * a.scale + logf(l) : -INFINITY;
+            tc_fence_before_sync();
+        } else {
+            failed = true;
+        }
+    }
+
+    if (failed && !aborted) atomicOr(&g_sm100_fwd2_status, 8u);
+    // Teardown: every thread gets here (all waits are bounded); the allocating warp frees TMEM.
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+cudaError_t launch_fwd2_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
+                              const Sm100FwdArgs &a, cudaStream_t stream) {
+    dim3 grid(a.pair_heads ? a.hq / 2 : a.hq, a.pair_heads ? (a.tq + BM - 1) / BM : (a.tq + NT * BM - 1) / (NT * BM), a.b);
+    cudaError_t e;
+    if (dtype == DASH_ATTN_BF16) {
+        e = cudaFuncSetAttribute(fwd2_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        fwd2_sm100_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
+    } else {
+        e = cudaFuncSetAttribute(fwd2_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        fwd2_sm100_kernel<__half><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t read_sm100_fwd2_status(unsigned int *status, bool clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_sm100_fwd2_status, sizeof(unsigned int));
+    if (e != cudaSuccess) return e;
+    if (clear && *status) {
+        unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_sm100_fwd2_status, &zero, sizeof(unsigned int));
+    }
+    return e;
+}
+
+}  // namespace dash

@@ -8,11 +8,13 @@
 //               issues the tcgen05 MMAs: S_j = Q K_j^T into the S buffer (j mod 2), O += P_j V_j;
 //   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S_j from tensor
 //               memory, mask what the row does not see, keep the online softmax in f32 with the
-//               scale folded into an exp2, write P_j rounded to the input dtype into shared memory
-//               in the layout of an MMA A operand, and at the end normalise O and store it with
-//               the row's log-sum-exp.
-// The S buffers and the P buffers are double, so QK^T of the next key tile runs under the softmax
-// of the current one, and P V of the current one under the softmax of the next.
+//               scale folded into an exp2, write P_j rounded to the input dtype back into tensor
+//               memory over the first half of the S buffer they read (two 16-bit values per
+//               32-bit column: the A operand of P V comes from tensor memory), and at the end
+//               normalise O and store it with the row's log-sum-exp.
+// The S buffer is double, so QK^T of the next key tile runs under the softmax of the current one,
+// and P V of the current one under the softmax of the next; a buffer is free for S_{j+2} once
+// P_j V_j has completed.
 //
 // The running maximum is "lazy": the accumulator is rescaled only when a row's maximum grows by
 // more than 2^8, otherwise the stale maximum stays the reference of the exponentials (their sum and
@@ -49,7 +51,7 @@ constexpr float RESCALE_LOG2 = 8.0f;
 
 struct Barriers {
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2];
-    uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_ready;
+    uint64_t s_full[2], s_empty[2], p_full[2], o_ready;
 };
 
 struct Shared {
@@ -59,7 +61,7 @@ struct Shared {
     unsigned int abort;
 };
 
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + 7 * TILE_BYTES /*Q, 2 K, 2 V, 2 P*/ + 1024 /*Shared*/;
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + 5 * TILE_BYTES /*Q, 2 K, 2 V*/ + 1024 /*Shared*/;
 
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
@@ -88,8 +90,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     uint8_t *q_s = smem;
     uint8_t *k_s = q_s + TILE_BYTES;
     uint8_t *v_s = k_s + 2 * TILE_BYTES;
-    uint8_t *p_s = v_s + 2 * TILE_BYTES;
-    Shared &sh = *reinterpret_cast<Shared *>(p_s + 2 * TILE_BYTES);
+    Shared &sh = *reinterpret_cast<Shared *>(v_s + 2 * TILE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x;
@@ -110,9 +111,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             mbar_init(BAR(sh.bar.v_full, i), 1);
             mbar_init(BAR(sh.bar.v_empty, i), 1);
             mbar_init(BAR(sh.bar.s_full, i), 1);
-            mbar_init(BAR(sh.bar.s_empty, i), 128);
+            mbar_init(BAR(sh.bar.s_empty, i), 1);
             mbar_init(BAR(sh.bar.p_full, i), 128);
-            mbar_init(BAR(sh.bar.p_empty, i), 1);
         }
         mbar_init(o_ready, 1);
         fence_mbar_init();
@@ -190,16 +190,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 // A = P: 16 keys = 32 bytes along the swizzled row, the second 64 keys in the second half.
                 // B = V: rows are keys (K of this product), 128 bytes of head dimension per row and half:
                 // 64-column atoms HALF_BYTES apart (leading), 8-key groups 1024 bytes apart.
-                const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s + st * TILE_BYTES), 16, 1024);
                 const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * TILE_BYTES), HALF_BYTES, 1024);
-                const uint32_t v_empty = BAR(sh.bar.v_empty, st), p_empty = BAR(sh.bar.p_empty, st);
+                const uint32_t v_empty = BAR(sh.bar.v_empty, st), s_empty = BAR(sh.bar.s_empty, st);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < BN / 16; ++ks)
-                        umma_f16(tmem + 256, desc_at(p_desc, (ks >> 2) * HALF_BYTES + (ks & 3) * 32), desc_at(v_desc, ks * 2048),
-                                 IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
+                        // A = P in tensor memory, over the S buffer it came from: 16 keys = 8 columns a step.
+                        umma_f16_ts(tmem + 256, tmem + st * BN + ks * 8, desc_at(v_desc, ks * 2048), IDESC_O,
+                                    (i > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(v_empty);
-                    umma_commit(p_empty);
+                    umma_commit(s_empty);   // the S buffer (now P) may be overwritten by S of tile i + 2
                     umma_commit(o_ready);
                 }
                 __syncwarp();
@@ -253,8 +253,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(t_lane + st * BN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             tmem_ld_wait();
-            tc_fence_before_sync();
-            mbar_arrive(BAR(sh.bar.s_empty, st));
 
             const bool clear = !padded && k0 >= lo && k0 + BN <= hi;  // the row sees the whole tile
             if (!__all_sync(0xffffffffu, clear)) {
@@ -288,9 +286,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
             const float neg = m_ref == -INFINITY ? 0.f : -m_ref * a.scale_log2;
 
-            // The P buffer is free once P V of tile j - 2 has completed.
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_empty, st), ph ^ 1))) { failed = true; break; }
-            uint8_t *p_row = p_s + st * TILE_BYTES + r * 128;
+            uint32_t pk[BN / 2];  // P of this row, two keys per 32-bit column
             const float2 sl2 = make_float2(a.scale_log2, a.scale_log2), neg2 = make_float2(neg, neg);
             float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
@@ -304,10 +300,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     p[2 * e + 1] = ex2(x.y);
                     sum2[e] = add2(sum2[e], make_float2(p[2 * e], p[2 * e + 1]));
                 }
-                uint4 v = make_uint4(Pack<T>::two(p[0], p[1]), Pack<T>::two(p[2], p[3]), Pack<T>::two(p[4], p[5]),
-                                     Pack<T>::two(p[6], p[7]));
-                // 16-byte chunk (cc mod 8) of the row's 128 bytes in half (cc / 8), XOR-swizzled by the row.
-                *reinterpret_cast<uint4 *>(p_row + (cc >> 3) * HALF_BYTES + (((cc & 7) ^ (r & 7)) << 4)) = v;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) pk[cc * 4 + e] = Pack<T>::two(p[2 * e], p[2 * e + 1]);
             }
             {
                 const float2 t = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
@@ -332,7 +326,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     tc_fence_before_sync();
                 }
             }
-            fence_proxy_async_smem();
+            // P goes back into the first 64 columns of the S buffer it was read from.
+            tmem_st32(t_lane + st * BN, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+            tmem_st32(t_lane + st * BN + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+            tmem_st_wait();
+            tc_fence_before_sync();
             mbar_arrive(BAR(sh.bar.p_full, st));
         }
 
@@ -407,9 +405,11 @@ cudaError_t read_sm100_status(unsigned int *status, bool clear) {
         e = cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(unsigned int));
         if (e != cudaSuccess) return e;
     }
-    unsigned int bwd = 0;
+    unsigned int bwd = 0, fwd2 = 0;
     e = read_sm100_bwd_status(&bwd, clear);
-    *status |= bwd;
+    if (e != cudaSuccess) return e;
+    e = read_sm100_fwd2_status(&fwd2, clear);
+    *status |= bwd | fwd2;
     return e;
 }
 

@@ -6,6 +6,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -106,10 +107,14 @@ size_t sm100_backward_workspace(const dash_attn_params *p) { return bwd_sm100_or
 
 cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *, cudaStream_t stream, int *launches,
                           std::string &err) {
+    // The two-tile kernel shares every K / V tile between two query tiles; DASH_ATTN_FWD_TILES=1
+    // keeps the one-tile kernel (for comparison runs).
+    static const bool one_tile = [] { const char *e = std::getenv("DASH_ATTN_FWD_TILES"); return e && std::atoi(e) == 1; }();
+    const int kv_rows = one_tile ? 128 : 64;
     CUtensorMap tq, tk, tv;
-    if (!encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride) ||
-        !encode(&tk, p->dtype, a.k.ptr, p->b, p->tk, p->hkv, p->k_stride) ||
-        !encode(&tv, p->dtype, a.v.ptr, p->b, p->tk, p->hkv, p->v_stride)) {
+    if (!encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride, 128) ||
+        !encode(&tk, p->dtype, a.k.ptr, p->b, p->tk, p->hkv, p->k_stride, kv_rows) ||
+        !encode(&tv, p->dtype, a.v.ptr, p->b, p->tk, p->hkv, p->v_stride, kv_rows)) {
         err = "attention: the driver refused a TMA tensor map over the inputs";
         return cudaSuccess;
     }
@@ -120,7 +125,8 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     f.out = a.out;
     f.lse = a.lse;
     f.mask = a.mask;
-    cudaError_t e = launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream);
+    f.pair_heads = ((p->hq / p->hkv) % 2 == 0) ? 1 : 0;
+    cudaError_t e = one_tile ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, f, stream);
     *launches += 1;
     return e;
 }

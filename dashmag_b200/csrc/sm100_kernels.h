@@ -15,6 +15,7 @@ struct Sm100FwdArgs {
     void *out;         // [B,Tq,Hq,128] contiguous, the inputs' dtype
     float *lse;        // [B,Tq,Hq]
     MaskArgs mask;
+    int pair_heads;    // two-tile kernel: the block's tiles are two heads of one group (else two row tiles)
 };
 
 struct Sm100BwdArgs {
@@ -40,6 +41,10 @@ size_t bwd_sm100_order_bytes(int b, int tk);
 
 cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                              const Sm100FwdArgs &a, cudaStream_t stream);
+// The two-tile forward: tq with boxes of 128 rows, tk / tv with boxes of 64 rows.
+cudaError_t launch_fwd2_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
+                              const Sm100FwdArgs &a, cudaStream_t stream);
+cudaError_t read_sm100_fwd2_status(unsigned int *status, bool clear);
 // Reads (and optionally clears) the sticky device word the kernels raise when a bounded wait ran
 // out.  Synchronises with the device.
 cudaError_t read_sm100_status(unsigned int *status, bool clear);

@@ -17,6 +17,10 @@ DEV = "cuda:0"
 # bf16 results against the f64 oracle: o, lse, dq, dk, dv relative to each part's largest value
 # (the bounds of test_kernels_gpu.OWN: one rounding of the dtype plus the rounded P / dS).
 TOL = [4.3e-3, 1e-6, 8.0e-3, 5.5e-3, 5.0e-3]
+# A single sampled query is normalised by the largest value of its own row only, which sits well
+# under the tensor's: P rounded to bf16 (2^-9 of sum p|v| / l, up to twice the row's largest output
+# over ~100 keys) plus the output's own rounding (2^-9).
+ROW_TOL = 8.0e-3
 
 
 def normal(shape, seed):
@@ -60,7 +64,7 @@ def check_sampled_rows(name, rows, cu, q, k, v, o, lse, window):
         lo = int(cu[s]) if window is None else max(int(cu[s]), i - window)
         wo, wl = oracle.numpy_forward(host(q[:, i:i + 1]), host(k[:, lo:i + 1]), host(v[:, lo:i + 1]))
         eo, el = rel(host(o[:, i:i + 1]), wo), rel(host(lse[:, i:i + 1]), wl)
-        assert eo <= TOL[0] and el <= TOL[1], f"{name} row {i} (keys {lo}..{i}): o {eo:.3e}, lse {el:.3e}"
+        assert eo <= ROW_TOL and el <= TOL[1], f"{name} row {i} (keys {lo}..{i}): o {eo:.3e}, lse {el:.3e}"
 
 
 def run(q, k, v, g, mask, options):
