@@ -4,11 +4,11 @@
 // repeat from run to run (the contract's default, crates/dash-contract/src/attention.rs:96-102):
 //
 //   dkdv   one block per (128 keys, key-value head).  K_j and V_j stay in shared memory; the block
-//          sweeps the query heads of the group and, in steps of 64, the queries that see the key
+//          sweeps the query heads of the group and, in steps of 128, the queries that see the key
 //          block.  Per step:  S^T = K_j Q^T and dP^T = V_j dO^T on the tensor cores (TMEM lane =
 //          key), P^T = exp2(S^T sl - lse) and dS^T = P^T (dP^T - delta) elementwise, rounded to the
-//          input dtype into shared memory, then dV += P^T dO and dK += dS^T Q, accumulated in TMEM
-//          over the whole sweep.
+//          input dtype back into tensor memory, then dV += P^T dO and dK += dS^T Q with the A
+//          operand read from tensor memory, accumulated in TMEM over the whole sweep.
 //   dq     one block per (128 queries, query head).  Q_i and dO_i stay in shared memory; the block
 //          sweeps, in steps of 64, the keys its queries see.  Per step: S = Q_i K^T, dP = dO_i V^T,
 //          dS = P (dP - delta), then dQ += dS K.
@@ -17,12 +17,12 @@
 // 128-deep products per pair of tiles.  The streamed tiles serve twice from one copy in shared
 // memory - K-major for the score products and MN-major for the gradient products - through two
 // descriptors over the same 128-byte-swizzled bytes.  Warp roles as in the forward: warp 0 issues
-// TMA loads (and, in dkdv, gathers the step's per-query log-sum-exp, delta and key interval),
-// warp 1 issues the MMAs and owns TMEM, warps 2..9 do the elementwise work: two warps per quadrant of
-// TMEM lanes, each thread one row (lane) and half of the step's columns, so that every scheduler
-// has two warps of it to interleave.
-// The score buffers and the P / dS buffers are double, so the products of one step run under the
-// elementwise work of its neighbours.  Every mbarrier wait is bounded (sm100_ptx.cuh).
+// TMA loads, warp 1 issues the MMAs and owns TMEM, the next 8 (dq) or 16 (dkdv) warps do the
+// elementwise work - two or four warps per quadrant of TMEM lanes, each thread one row (lane) and
+// a slice of the step's columns, so that every scheduler has several warps of it to interleave -
+// and in dkdv one more warp gathers the step's per-query log-sum-exp, delta and key interval, one
+// step ahead of their use (its loads from global memory were the longest link of the step before
+// they were issued early).  Every mbarrier wait is bounded (sm100_ptx.cuh).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -49,14 +49,19 @@ constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes
 constexpr int STEP_BYTES = STEP * HD * 2;  // 16 KiB
 constexpr int STEP_HALF = STEP_BYTES / 2;  // 64 rows of 128 bytes
 constexpr int PS_BYTES = BIG * STEP * 2;   // 16 KiB: a P^T / dS^T / dS tile, 128 rows of 128 bytes
+constexpr int QS = 128;                    // dkdv: queries per step
 constexpr int CG = 2;                      // elementwise warps per TMEM lane quadrant: each takes STEP / CG columns
 constexpr int CW = STEP / CG;              // columns of a step per elementwise thread
+constexpr int QW = QS / CG;                // dkdv: queries of a step per elementwise thread
 constexpr int EW_WARPS = 4 * CG;           // elementwise warps: warps 2 .. 2 + EW_WARPS - 1
 constexpr int EW_THREADS = 32 * EW_WARPS;
 constexpr int AUX_WARP = 2 + EW_WARPS;     // dkdv: one more warp gathers the per-query vectors
 constexpr int THREADS = 32 * (2 + EW_WARPS);        // dq
 constexpr int THREADS_DKDV = 32 * (3 + EW_WARPS);   // dkdv
 constexpr float LOG2E = 1.4426950408889634f;
+
+// 2^x on the special-function pipe or, for a share of the elements, on the FMA pipe.
+template <bool POLY> __device__ __forceinline__ float exp2_mixed(float x) { return POLY ? ex2_poly3(x) : ex2(x); }
 
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
@@ -112,12 +117,12 @@ __device__ __forceinline__ void store_acc_cols(uint32_t taddr, T *dst, float sca
     }
 }
 
-// HD / CG zero elements.
-template <typename T>
+// 8 * CHUNKS zero elements.
+template <typename T, int CHUNKS = 16 / CG>
 __device__ __forceinline__ void store_zero_cols(T *dst) {
     const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int c = 0; c < 16 / CG; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
+    for (int c = 0; c < CHUNKS; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
 }
 
 // The queries [first, end) that may see some key of [k0, k1): a superset cut from the closed form
@@ -201,7 +206,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) bwd_plan_kernel(const Sm100BwdAr
         const int kt = i % nkb, k0 = kt * BIG;
         int first, end;
         query_range(a.mask, k0, min(k0 + BIG, a.tk), a.tq, a.tk, first, end);
-        work[i] = end > first ? (end - (first / STEP) * STEP + STEP - 1) / STEP : 0;
+        work[i] = end > first ? (end - first + QS - 1) / QS : 0;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < items; i += PLAN_THREADS) {
@@ -223,19 +228,62 @@ size_t bwd_sm100_order_bytes(int b, int tk) {
 // =================================================================================================
 // dK, dV
 // =================================================================================================
+// Steps of 128 queries, so that all four products of a step are 128 x 128 x 128 (the width at which
+// the tensor cores run at full rate).  The score tiles are single in tensor memory and P^T / dS^T are
+// written over the f32 values they were made from (two 16-bit values per 32-bit column) and fed to
+// dV += P^T dO and dK += dS^T Q as A operands straight from tensor memory; MMAs of one thread
+// execute in issue order, which is what lets S^T of the next step be issued right behind the
+// product that reads P^T from the same columns.  Issue order per step t:
+//     dV(t)  S^T(t+1)  dK(t)  dP^T(t+1)
+// so the P half of the elementwise work of step t+1 runs under dK(t) and dP^T(t+1), and its dS half
+// under dV(t+1) and S^T(t+2).
+constexpr int POLY_OF4 = 1;                     // of every four exponentials, how many run on the FMA pipe (ex2_poly3)
+constexpr int KCG = 4;                          // elementwise warps per TMEM lane quadrant
+constexpr int KQW = QS / KCG;                   // queries of a step per elementwise thread
+constexpr int KEW_THREADS = 32 * 4 * KCG;
+constexpr int KAUX_WARP = 2 + 4 * KCG;
+constexpr int KTHREADS = 32 * (3 + 4 * KCG);
+static_assert(KQW == 32, "one 32-column TMEM load per thread and phase");
+
+struct DkdvBarriers {
+    uint64_t res_full;
+    uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+    uint64_t aux_full[2];
+    uint64_t s_full, p_full, dp_full, ds_full;
+    uint64_t acc_ready;
+};
+
+struct alignas(16) QAux {   // what the elementwise threads need per query of a step
+    float lse2[QS];        // log-sum-exp in base 2, +inf for a query that saw no key or is out of range
+    float delta[QS];
+    int lo[QS], hi[QS];
+    int clear;             // every query of the step sees every key of the block
+};
+
+struct DkdvTail {
+    DkdvBarriers bar;
+    QAux aux[2];
+    uint32_t tmem_base;
+    unsigned int abort;
+    int cu_q[CU_CACHE], cu_k[CU_CACHE];   // the packed sequences' offsets, when they fit
+};
+
+constexpr size_t DKDV_TAIL = 12288;
+static_assert(sizeof(DkdvTail) <= DKDV_TAIL, "the tail of the dkdv kernel's shared memory");
+// 1 KiB slack | K, V resident (2 x 32 KiB) | Q ring 2 x 32 KiB | dO ring 2 x 32 KiB | tail
+constexpr size_t SMEM_DKDV = 1024 + 6 * BIG_BYTES + DKDV_TAIL;
+
 template <typename T>
-__global__ void __launch_bounds__(THREADS_DKDV, 1)
+__global__ void __launch_bounds__(KTHREADS, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const Sm100BwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *k_s = smem, *v_s = k_s + BIG_BYTES;
-    uint8_t *q_s = v_s + BIG_BYTES;           // [2][STEP_BYTES]
-    uint8_t *do_s = q_s + 2 * STEP_BYTES;     // [2][STEP_BYTES]
-    uint8_t *pt_s = do_s + 2 * STEP_BYTES;    // [2][PS_BYTES]
-    uint8_t *ds_s = pt_s + 2 * PS_BYTES;      // [2][PS_BYTES]
-    SharedTail &sh = *reinterpret_cast<SharedTail *>(ds_s + 2 * PS_BYTES);
+    uint8_t *q_s = v_s + BIG_BYTES;           // [2][BIG_BYTES]
+    uint8_t *do_s = q_s + 2 * BIG_BYTES;      // [2][BIG_BYTES]
+    DkdvTail &sh = *reinterpret_cast<DkdvTail *>(do_s + 2 * BIG_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Key blocks are taken in the order the plan kernel left: the ones most queries see first, so
@@ -251,14 +299,16 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
         mbar_init(BAR(sh.bar.res_full), 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(sh.bar.str_full[i]), 1);
-            mbar_init(BAR(sh.bar.str_empty[i]), 1);
-            mbar_init(BAR(sh.bar.aux_full[i]), 32);
-            mbar_init(BAR(sh.bar.sc_full[i]), 1);
-            mbar_init(BAR(sh.bar.sc_empty[i]), EW_THREADS);
-            mbar_init(BAR(sh.bar.ps_full[i]), EW_THREADS);
-            mbar_init(BAR(sh.bar.ps_empty[i]), 1);
+            mbar_init(BAR(sh.bar.q_full[i]), 1);
+            mbar_init(BAR(sh.bar.q_empty[i]), 1);
+            mbar_init(BAR(sh.bar.do_full[i]), 1);
+            mbar_init(BAR(sh.bar.do_empty[i]), 1);
+            mbar_init(BAR(sh.bar.aux_full[i]), 1);
         }
+        mbar_init(BAR(sh.bar.s_full), 1);
+        mbar_init(BAR(sh.bar.dp_full), 1);
+        mbar_init(BAR(sh.bar.p_full), 4 * KCG);   // one arrival per elementwise warp
+        mbar_init(BAR(sh.bar.ds_full), 4 * KCG);
         mbar_init(BAR(sh.bar.acc_ready), 1);
         fence_mbar_init();
         prefetch_tensormap(&tm_k);
@@ -290,11 +340,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     tc_fence_after_sync();
     const uint32_t tmem = sh.tmem_base;
     const bool aborted = sh.abort != 0;
-    const int q_begin = (qfirst / STEP) * STEP;
-    const int tiles = (!aborted && qend > qfirst) ? (qend - q_begin + STEP - 1) / STEP : 0;
+    const int tiles = (!aborted && qend > qfirst) ? (qend - qfirst + QS - 1) / QS : 0;
     const int steps = tiles * group;
     bool failed = aborted;
-    // TMEM columns: S^T[2] at 0 / 64, dP^T[2] at 128 / 192, dV at 256, dK at 384.
+    // TMEM columns: S^T at 0, dP^T at 128 (each with its 16-bit twin over the first half of every
+    // group of 32 columns: columns 32 g + [0, 16) hold queries 32 g + [0, 32)), dV at 256, dK at 384.
     constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
 
     if (warp == 0) {
@@ -308,46 +358,61 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, rfull, 64, hk, k0, b);
             for (int t = 0; t < steps; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1;
-                const int h = hk * group + t / tiles, q0 = q_begin + (t % tiles) * STEP;
-                if (!mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1)) { failed = true; break; }
-                const uint32_t full = BAR(sh.bar.str_full[st]);
-                const uint32_t qd = smem_u32(q_s + st * STEP_BYTES), gd = smem_u32(do_s + st * STEP_BYTES);
-                mbar_expect_tx(full, 2 * STEP_BYTES);
-                tma_load_4d(qd, &tm_q, full, 0, h, q0, b);
-                tma_load_4d(qd + STEP_HALF, &tm_q, full, 64, h, q0, b);
-                tma_load_4d(gd, &tm_do, full, 0, h, q0, b);
-                tma_load_4d(gd + STEP_HALF, &tm_do, full, 64, h, q0, b);
+                const int h = hk * group + t / tiles, q0 = qfirst + (t % tiles) * QS;
+                // Q first (S^T of the step is issued before dP^T); its stage is also the later to come free.
+                if (!mbar_wait(BAR(sh.bar.q_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t qf = BAR(sh.bar.q_full[st]), qd = smem_u32(q_s + st * BIG_BYTES);
+                mbar_expect_tx(qf, BIG_BYTES);
+                tma_load_4d(qd, &tm_q, qf, 0, h, q0, b);
+                tma_load_4d(qd + BIG_HALF, &tm_q, qf, 64, h, q0, b);
+                if (!mbar_wait(BAR(sh.bar.do_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t gf = BAR(sh.bar.do_full[st]), gd = smem_u32(do_s + st * BIG_BYTES);
+                mbar_expect_tx(gf, BIG_BYTES);
+                tma_load_4d(gd, &tm_do, gf, 0, h, q0, b);
+                tma_load_4d(gd + BIG_HALF, &tm_do, gf, 64, h, q0, b);
             }
         }
-    } else if (warp == AUX_WARP) {
+    } else if (warp == KAUX_WARP) {
         // ---------------- the per-query vectors of each step: log-sum-exp, delta, key interval ----------------
+        // The gathers of step t + 1 are issued (all of them, from clamped rows, before anything
+        // looks at their values) ahead of the work on step t, so that no step waits for a trip to L2.
+        constexpr int RPL = QS / 32;   // rows per lane
+        float lse_n[RPL], dl_n[RPL];
+        auto gather = [&](int t) {
+            const int h = hk * group + t / tiles, q0 = qfirst + (t % tiles) * QS;
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                const int q = min(q0 + lane + 32 * i, a.tq - 1);
+                const int64_t at = ((int64_t)b * a.tq + q) * a.hq + h;
+                lse_n[i] = a.lse[at];
+                dl_n[i] = a.delta[at];
+            }
+        };
+        if (steps > 0) gather(0);
         for (int t = 0; t < steps; ++t) {
             const int st = t & 1, ph = (t >> 1) & 1;
-            const int h = hk * group + t / tiles, q0 = q_begin + (t % tiles) * STEP;
-            // Gather first (loads and the interval search depend on the step alone), wait after: the
-            // latency of the gathering hides behind the wait for the stage.
-            float l2v[2], dlv[2];
-            int lov[2], hiv[2];
+            const int q0 = qfirst + (t % tiles) * QS;
+            float lse_c[RPL], dl_c[RPL];
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) { lse_c[i] = lse_n[i]; dl_c[i] = dl_n[i]; }
+            if (t + 1 < steps) gather(t + 1);
+            float l2v[RPL], dlv[RPL];
+            int lov[RPL], hiv[RPL];
             bool clear = true;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < RPL; ++i) {
                 const int q = q0 + lane + 32 * i;
-                l2v[i] = INFINITY;
-                dlv[i] = 0.f;
-                if (q < a.tq) {
-                    const int64_t at = ((int64_t)b * a.tq + q) * a.hq + h;
-                    const float x = a.lse[at];
-                    l2v[i] = x == -INFINITY ? INFINITY : x * LOG2E;
-                    dlv[i] = a.delta[at];
-                }
+                const bool in = q < a.tq;
+                l2v[i] = (!in || lse_c[i] == -INFINITY) ? INFINITY : lse_c[i] * LOG2E;
+                dlv[i] = in ? dl_c[i] : 0.f;
                 row_bounds(qmask, q, a.tq, a.tk, lov[i], hiv[i]);
                 clear = clear && lov[i] <= k0 && hiv[i] >= k0 + BIG;
             }
-            // aux[st] is free when the stage is: the elementwise threads of step t - 2 are done with it.
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1))) { failed = true; break; }
-            StepAux &aux = sh.aux[st];
+            // aux[st] is free when the Q stage is: the elementwise threads of step t - 2 are done with it.
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_empty[st]), ph ^ 1))) { failed = true; break; }
+            QAux &aux = sh.aux[st];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < RPL; ++i) {
                 const int c = lane + 32 * i;
                 aux.lse2[c] = l2v[i];
                 aux.delta[c] = dlv[i];
@@ -357,123 +422,166 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             clear = __all_sync(0xffffffffu, clear) && a.mask.kind != 1;
             if (lane == 0) aux.clear = clear ? 1 : 0;
             __syncwarp();
-            mbar_arrive(BAR(sh.bar.aux_full[st]));
+            if (lane == 0) mbar_arrive(BAR(sh.bar.aux_full[st]));
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
         if (steps > 0) {
-            constexpr uint32_t IDESC_SC = idesc_f16(BIG, STEP, Pack<T>::FMT, 0, 0);   // [128 keys x 64 queries]
+            constexpr uint32_t IDESC_SC = idesc_f16(BIG, QS, Pack<T>::FMT, 0, 0);     // [128 keys x 128 queries]
             constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 keys x 128 d], B MN-major
             const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s), 16, 1024), v_desc = smem_desc_sw128(smem_u32(v_s), 16, 1024);
-            auto grads = [&](int i) -> bool {
-                const int st = i & 1, ph = (i >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_full[st]), ph))) return false;
+            // The 16 queries of k-step ks of a gradient product, as 16-bit pairs in tensor memory.
+            auto a_cols = [](int ks) { return static_cast<uint32_t>(32 * (ks >> 1) + 8 * (ks & 1)); };
+            auto scores = [&](int t) -> bool {   // S^T(t) = K Q^T
+                const int st = t & 1, ph = (t >> 1) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_full[st]), ph))) return false;
                 tc_fence_after_sync();
-                const uint64_t pt = smem_desc_sw128(smem_u32(pt_s + st * PS_BYTES), 16, 1024);
-                const uint64_t ds = smem_desc_sw128(smem_u32(ds_s + st * PS_BYTES), 16, 1024);
-                // The streamed tiles as MN-major B operands: rows are the K of these products.
-                const uint64_t qm = smem_desc_sw128(smem_u32(q_s + st * STEP_BYTES), STEP_HALF, 1024);
-                const uint64_t gm = smem_desc_sw128(smem_u32(do_s + st * STEP_BYTES), STEP_HALF, 1024);
-                const uint32_t e0 = BAR(sh.bar.str_empty[st]), e1 = BAR(sh.bar.ps_empty[st]);
+                const uint64_t qk = smem_desc_sw128(smem_u32(q_s + st * BIG_BYTES), 16, 1024);
+                const uint32_t full = BAR(sh.bar.s_full);
                 if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < STEP / 16; ++ks)   // dV += P^T dO over 64 queries
-                        umma_f16(tmem + COL_DV, desc_at(pt, ks * 32), desc_at(gm, ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < HD / 16; ++ks)
+                        umma_f16(tmem + COL_ST, desc_at(k_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(qk, (ks >> 2) * BIG_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    umma_commit(full);
+                }
+                __syncwarp();
+                return true;
+            };
+            auto dscores = [&](int t) -> bool {  // dP^T(t) = V dO^T
+                const int st = t & 1, ph = (t >> 1) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.do_full[st]), ph))) return false;
+                tc_fence_after_sync();
+                const uint64_t gk = smem_desc_sw128(smem_u32(do_s + st * BIG_BYTES), 16, 1024);
+                const uint32_t full = BAR(sh.bar.dp_full);
+                if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < STEP / 16; ++ks)   // dK += dS^T Q
-                        umma_f16(tmem + COL_DK, desc_at(ds, ks * 32), desc_at(qm, ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(e0);
-                    umma_commit(e1);
+                    for (int ks = 0; ks < HD / 16; ++ks)
+                        umma_f16(tmem + COL_DPT, desc_at(v_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(gk, (ks >> 2) * BIG_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    umma_commit(full);
                 }
                 __syncwarp();
                 return true;
             };
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.res_full), 0))) failed = true;
+            if (!failed && !(scores(0) && dscores(0))) failed = true;
             for (int t = 0; t < steps && !failed; ++t) {
-                const int st = t & 1, ph = (t >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_full[st]), ph) && mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1))) {
-                    failed = true;
-                    break;
-                }
+                const int st = t & 1, ph = t & 1;
+                // dV += P^T dO over the step's 128 queries; the dO stage is free behind it.
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full), ph))) { failed = true; break; }
                 tc_fence_after_sync();
-                const uint64_t qk = smem_desc_sw128(smem_u32(q_s + st * STEP_BYTES), 16, 1024);
-                const uint64_t gk = smem_desc_sw128(smem_u32(do_s + st * STEP_BYTES), 16, 1024);
-                const uint32_t full = BAR(sh.bar.sc_full[st]);
-                if (elect_one()) {
+                {
+                    const uint64_t gm = smem_desc_sw128(smem_u32(do_s + st * BIG_BYTES), BIG_HALF, 1024);
+                    const uint32_t e = BAR(sh.bar.do_empty[st]);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks)   // S^T = K Q^T
-                        umma_f16(tmem + COL_ST + st * STEP, desc_at(k_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                                 desc_at(qk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
-#pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks)   // dP^T = V dO^T
-                        umma_f16(tmem + COL_DPT + st * STEP, desc_at(v_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                                 desc_at(gk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
-                    umma_commit(full);
+                        for (int ks = 0; ks < QS / 16; ++ks)
+                            umma_f16_ts(tmem + COL_DV, tmem + COL_ST + a_cols(ks), desc_at(gm, ks * 2048), IDESC_ACC,
+                                        (t > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(e);
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
-                if (t > 0 && !grads(t - 1)) { failed = true; break; }
+                if (t + 1 < steps && !scores(t + 1)) { failed = true; break; }
+                // dK += dS^T Q; the Q stage is free behind it.
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ds_full), ph))) { failed = true; break; }
+                tc_fence_after_sync();
+                {
+                    const uint64_t qm = smem_desc_sw128(smem_u32(q_s + st * BIG_BYTES), BIG_HALF, 1024);
+                    const uint32_t e = BAR(sh.bar.q_empty[st]);
+                    if (elect_one()) {
+#pragma unroll
+                        for (int ks = 0; ks < QS / 16; ++ks)
+                            umma_f16_ts(tmem + COL_DK, tmem + COL_DPT + a_cols(ks), desc_at(qm, ks * 2048), IDESC_ACC,
+                                        (t > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(e);
+                    }
+                    __syncwarp();
+                }
+                if (t + 1 < steps && !dscores(t + 1)) { failed = true; break; }
             }
-            if (!failed && !grads(steps - 1)) failed = true;
             if (!failed && elect_one()) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
-        // ---------------- elementwise: a key row and CW of the step's columns per thread ----------------
+        // ---------------- elementwise: a key row and 32 of the step's queries per thread ----------------
         const int lane_base = 32 * (warp & 3);
-        const int cg = (warp - 2) >> 2, col0 = cg * CW;
+        const int cg = (warp - 2) >> 2, col0 = cg * KQW;
         const int r = lane_base + lane;
         const int key = k0 + r;
         const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
         const bool open = key < a.tk && !key_padded(a.mask, b, key);
         for (int t = 0; t < steps && !failed; ++t) {
-            const int st = t & 1, ph = (t >> 1) & 1;
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.aux_full[st]), ph) && mbar_wait(BAR(sh.bar.sc_full[st]), ph))) {
+            const int st = t & 1, aph = (t >> 1) & 1, ph = t & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.aux_full[st]), aph) && mbar_wait(BAR(sh.bar.s_full), ph))) {
                 failed = true;
                 break;
             }
             tc_fence_after_sync();
-            float s[CW], dp[CW];
-            tmem_ld32(t_lane + COL_ST + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld32(t_lane + COL_DPT + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+            float p[KQW];
+            tmem_ld32(t_lane + COL_ST + col0, *reinterpret_cast<uint32_t(*)[32]>(&p[0]));
             tmem_ld_wait();
-            tc_fence_before_sync();
-            mbar_arrive(BAR(sh.bar.sc_empty[st]));
-
-            const StepAux &aux = sh.aux[st];
+            const QAux &aux = sh.aux[st];
             if (aux.clear == 0) {
                 // A step that cuts some query's interval (or has padded keys): hide what this key
                 // is not seen by before the exponentials, in a pass of its own so that the common,
                 // unmasked step pays nothing for it.
 #pragma unroll
-                for (int c = 0; c < CW; ++c)
-                    s[c] = (open && key >= aux.lo[col0 + c] && key < aux.hi[col0 + c]) ? s[c] : -INFINITY;
+                for (int c = 0; c < KQW; ++c)
+                    p[c] = (open && key >= aux.lo[col0 + c] && key < aux.hi[col0 + c]) ? p[c] : -INFINITY;
             }
+            {
+                uint32_t pk[KQW / 2];
 #pragma unroll
-            for (int c4 = 0; c4 < CW / 4; ++c4) {
-                const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[col0 + c4 * 4]);
-                const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[col0 + c4 * 4]);
-                const float l2v[4] = {l2.x, l2.y, l2.z, l2.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int c = c4 * 4 + e;
-                    const float p = ex2(fmaf(s[c], a.scale_log2, -l2v[e]));
-                    s[c] = p;
-                    dp[c] = p * (dp[c] - dlv[e]);
+                for (int c4 = 0; c4 < KQW / 4; ++c4) {
+                    const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[col0 + c4 * 4]);
+                    p[c4 * 4 + 0] = exp2_mixed<(POLY_OF4 > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2.x));
+                    p[c4 * 4 + 1] = exp2_mixed<(POLY_OF4 > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2.y));
+                    p[c4 * 4 + 2] = exp2_mixed<(POLY_OF4 > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2.z));
+                    p[c4 * 4 + 3] = exp2_mixed<(POLY_OF4 > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2.w));
+                    pk[c4 * 2 + 0] = Pack<T>::two(p[c4 * 4 + 0], p[c4 * 4 + 1]);
+                    pk[c4 * 2 + 1] = Pack<T>::two(p[c4 * 4 + 2], p[c4 * 4 + 3]);
                 }
+                // P^T over the first half of the f32 columns this thread has just read.
+                tmem_st16(t_lane + COL_ST + col0, pk);
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
-            store_row_cols<T>(pt_s + st * PS_BYTES, r, cg, s);
-            store_row_cols<T>(ds_s + st * PS_BYTES, r, cg, dp);
-            fence_proxy_async_smem();
-            mbar_arrive(BAR(sh.bar.ps_full[st]));
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.p_full));
+
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full), ph))) { failed = true; break; }
+            tc_fence_after_sync();
+            {
+                float dp[KQW];
+                tmem_ld32(t_lane + COL_DPT + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+                tmem_ld_wait();
+                uint32_t dk[KQW / 2];
+#pragma unroll
+                for (int c4 = 0; c4 < KQW / 4; ++c4) {
+                    const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[col0 + c4 * 4]);
+                    const float d0 = p[c4 * 4 + 0] * (dp[c4 * 4 + 0] - dl.x);
+                    const float d1 = p[c4 * 4 + 1] * (dp[c4 * 4 + 1] - dl.y);
+                    const float d2 = p[c4 * 4 + 2] * (dp[c4 * 4 + 2] - dl.z);
+                    const float d3 = p[c4 * 4 + 3] * (dp[c4 * 4 + 3] - dl.w);
+                    dk[c4 * 2 + 0] = Pack<T>::two(d0, d1);
+                    dk[c4 * 2 + 1] = Pack<T>::two(d2, d3);
+                }
+                tmem_st16(t_lane + COL_DPT + col0, dk);   // dS^T likewise
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full));
         }
-        // ---------------- epilogue: each thread its HD / CG columns of the row ----------------
-        constexpr int EC = HD / CG;
+        // ---------------- epilogue: each thread its HD / KCG columns of the row ----------------
+        constexpr int EC = HD / KCG;
         T *dk = static_cast<T *>(a.dk) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD + cg * EC;
         T *dv = static_cast<T *>(a.dv) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD + cg * EC;
         if (steps == 0 || failed) {
             if (key < a.tk && !failed) {
-                store_zero_cols(dk);
-                store_zero_cols(dv);
+                store_zero_cols<T, 16 / KCG>(dk);
+                store_zero_cols<T, 16 / KCG>(dv);
             }
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             tc_fence_after_sync();
@@ -706,7 +814,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 // -------------------------------------------------------------------------------------------------
 template <typename T>
 static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t stream, int *launches) {
-    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DKDV);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return e;
@@ -724,7 +832,7 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t 
     }
     if (items > 65535) return cudaErrorInvalidConfiguration;
     dim3 gk(a.hkv, (unsigned)items, 1);
-    bwd_dkdv_sm100_kernel<T><<<gk, THREADS_DKDV, SMEM_BYTES, stream>>>(m.k128, m.v128, m.q64, m.do64, a);
+    bwd_dkdv_sm100_kernel<T><<<gk, KTHREADS, SMEM_DKDV, stream>>>(m.k128, m.v128, m.q128, m.do128, a);
     *launches += 1;
     return cudaGetLastError();
 }

@@ -136,6 +136,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- tcgen05 MMA -----------------------------------------------------------------------------------
@@ -224,6 +233,23 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x for x <= 0 without the special-function pipe (ten issue slots of the FMA / ALU pipes against
+// one of the MUFU pipe, which takes a warp instruction every eight cycles): round to the nearest
+// integer by the magic-number add, a cubic
+// in the fraction (|f| <= 0.5; relative error 7.6e-5, a thirtieth of a bf16 step, so only for
+// values that are rounded to 16 bits right away), and the integer added into the exponent field.
+// Inputs below -126 (masked scores are -inf) give exactly zero.
+__device__ __forceinline__ float ex2_poly3(float x) {
+    const float xc = fmaxf(x, -126.f);
+    const float r = xc + 12582912.f;           // 1.5 * 2^23: the integer part lands in the low mantissa bits
+    const float f = xc - (r - 12582912.f);
+    float p = fmaf(f, 0.05520550534129143f, 0.24261397123336792f);
+    p = fmaf(p, f, 0.6932547688484192f);
+    p = fmaf(p, f, 0.9999276995658875f);
+    const float y = __uint_as_float(__float_as_uint(p) + (__float_as_uint(r) << 23));
+    return x < -126.f ? 0.f : y;   // exactly zero for what is masked (-inf), as the hardware exponential gives
 }
 
 }  // namespace ptx

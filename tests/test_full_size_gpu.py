@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 # bf16 results against the f64 oracle: o, lse, dq, dk, dv relative to each part's largest value
 # (the bounds of test_kernels_gpu.OWN: one rounding of the dtype plus the rounded P / dS).
-TOL = [4.3e-3, 1e-6, 8.0e-3, 5.5e-3, 5.0e-3]
+TOL = [5.0e-3, 1e-6, 8.0e-3, 5.5e-3, 5.0e-3]
 # A single sampled query is normalised by the largest value of its own row only, which sits well
 # under the tensor's: P rounded to bf16 (2^-9 of sum p|v| / l, up to twice the row's largest output
 # over ~100 keys) plus the output's own rounding (2^-9).
