@@ -41,23 +41,18 @@ __device__ unsigned int g_sm100_bwd_status = 0;
 
 namespace {
 
-constexpr int BIG = 128;                   // rows of the resident tile (and TMEM lanes)
-constexpr int STEP = 64;                   // rows of a streamed tile
+constexpr int BIG = 128;                   // rows of a tile: resident or streamed (and TMEM lanes)
 constexpr int HD = 128;
 constexpr int BIG_BYTES = BIG * HD * 2;    // 32 KiB
-constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes
-constexpr int STEP_BYTES = STEP * HD * 2;  // 16 KiB
-constexpr int STEP_HALF = STEP_BYTES / 2;  // 64 rows of 128 bytes
-constexpr int PS_BYTES = BIG * STEP * 2;   // 16 KiB: a P^T / dS^T / dS tile, 128 rows of 128 bytes
-constexpr int QS = 128;                    // dkdv: queries per step
-constexpr int CG = 2;                      // elementwise warps per TMEM lane quadrant: each takes STEP / CG columns
-constexpr int CW = STEP / CG;              // columns of a step per elementwise thread
-constexpr int QW = QS / CG;                // dkdv: queries of a step per elementwise thread
-constexpr int EW_WARPS = 4 * CG;           // elementwise warps: warps 2 .. 2 + EW_WARPS - 1
-constexpr int EW_THREADS = 32 * EW_WARPS;
-constexpr int AUX_WARP = 2 + EW_WARPS;     // dkdv: one more warp gathers the per-query vectors
-constexpr int THREADS = 32 * (2 + EW_WARPS);        // dq
-constexpr int THREADS_DKDV = 32 * (3 + EW_WARPS);   // dkdv
+constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes: the tile's first 64 columns
+constexpr int QS = BIG;                    // rows of a streamed tile: a step
+constexpr int POLY_OF4 = 1;                // of every four exponentials, how many run on the FMA pipe (ex2_poly3)
+constexpr int KCG = 4;                     // elementwise warps per TMEM lane quadrant
+constexpr int KQW = QS / KCG;              // columns of a step per elementwise thread
+constexpr int KEW_THREADS = 32 * 4 * KCG;
+constexpr int KAUX_WARP = 2 + 4 * KCG;     // dkdv: one more warp gathers the per-query vectors
+constexpr int KTHREADS = 32 * (3 + 4 * KCG);
+static_assert(KQW == 32, "one 32-column TMEM load per thread and phase");
 constexpr float LOG2E = 1.4426950408889634f;
 
 // 2^x on the special-function pipe or, for a share of the elements, on the FMA pipe.
@@ -78,20 +73,6 @@ template <> struct Pack<__half> {
         return *reinterpret_cast<uint32_t *>(&v);
     }
 };
-
-// Columns [cg * CW, (cg + 1) * CW) of row `r` of a [128 x 64] 16-bit tile in the layout of a K-major
-// MMA operand: 128 bytes per row, 16-byte chunks XOR-swizzled by the row.
-template <typename T>
-__device__ __forceinline__ void store_row_cols(uint8_t *tile, int r, int cg, const float (&x)[CW]) {
-    uint8_t *row = tile + r * 128;
-#pragma unroll
-    for (int i = 0; i < CW / 8; ++i) {
-        const int cc = cg * (CW / 8) + i;
-        uint4 v = make_uint4(Pack<T>::two(x[i * 8 + 0], x[i * 8 + 1]), Pack<T>::two(x[i * 8 + 2], x[i * 8 + 3]),
-                             Pack<T>::two(x[i * 8 + 4], x[i * 8 + 5]), Pack<T>::two(x[i * 8 + 6], x[i * 8 + 7]));
-        *reinterpret_cast<uint4 *>(row + ((cc ^ (r & 7)) << 4)) = v;
-    }
-}
 
 // `groups` x 32 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as
 // contiguous elements of the row.
@@ -118,7 +99,7 @@ __device__ __forceinline__ void store_acc_cols(uint32_t taddr, T *dst, float sca
 }
 
 // 8 * CHUNKS zero elements.
-template <typename T, int CHUNKS = 16 / CG>
+template <typename T, int CHUNKS>
 __device__ __forceinline__ void store_zero_cols(T *dst) {
     const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
@@ -157,35 +138,6 @@ __device__ __forceinline__ void query_range(const MaskArgs &m, int k0, int k1, i
 }
 
 constexpr int CU_CACHE = 768;   // offsets of packed sequences kept in shared memory (dkdv)
-
-struct PipeBarriers {
-    uint64_t res_full;               // the resident tiles have landed
-    uint64_t str_full[2], str_empty[2];  // streamed tiles
-    uint64_t aux_full[2];            // dkdv: per-query vectors of the step
-    uint64_t sc_full[2], sc_empty[2];    // score buffers in TMEM
-    uint64_t ps_full[2], ps_empty[2];    // P^T / dS^T (or dS) in shared memory
-    uint64_t acc_ready;
-};
-
-struct alignas(16) StepAux {  // dkdv: what the elementwise threads need per query of the step
-    float lse2[STEP];     // log-sum-exp in base 2, +inf for a query that saw no key or is out of range
-    float delta[STEP];
-    int lo[STEP], hi[STEP];
-    int clear;            // every query of the step sees every key of the block
-};
-
-struct SharedTail {
-    PipeBarriers bar;
-    StepAux aux[2];
-    uint32_t tmem_base;
-    unsigned int abort;
-    int red_lo[4], red_hi[4];
-    int cu_q[CU_CACHE], cu_k[CU_CACHE];   // dkdv: the packed sequences' offsets, when they fit
-};
-
-// shared memory: 1 KiB slack | resident A, resident B (2 x 32 KiB) | stream ring 2 x (16 + 16 KiB) |
-// P/dS ring 2 x (16 + 16 KiB) | tail
-constexpr size_t SMEM_BYTES = 1024 + 2 * BIG_BYTES + 4 * STEP_BYTES + 4 * PS_BYTES + 10240;
 
 }  // namespace
 
@@ -237,14 +189,6 @@ size_t bwd_sm100_order_bytes(int b, int tk) {
 //     dV(t)  S^T(t+1)  dK(t)  dP^T(t+1)
 // so the P half of the elementwise work of step t+1 runs under dK(t) and dP^T(t+1), and its dS half
 // under dV(t+1) and S^T(t+2).
-constexpr int POLY_OF4 = 1;                     // of every four exponentials, how many run on the FMA pipe (ex2_poly3)
-constexpr int KCG = 4;                          // elementwise warps per TMEM lane quadrant
-constexpr int KQW = QS / KCG;                   // queries of a step per elementwise thread
-constexpr int KEW_THREADS = 32 * 4 * KCG;
-constexpr int KAUX_WARP = 2 + 4 * KCG;
-constexpr int KTHREADS = 32 * (3 + 4 * KCG);
-static_assert(KQW == 32, "one 32-column TMEM load per thread and phase");
-
 struct DkdvBarriers {
     uint64_t res_full;
     uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
@@ -605,18 +549,45 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 // =================================================================================================
 // dQ
 // =================================================================================================
+// Steps of 128 keys: S = Q_i K^T and dP = dO_i V^T are 128 x 128 x 128 products, dS is written over
+// the f32 dP it was made from (two 16-bit values per 32-bit column) and dQ += dS K reads it from
+// tensor memory.  S is single in tensor memory - the elementwise threads take it into registers at
+// the start of a step, which frees it for the next step's product - and dP is double, so that both
+// score products of step t + 1 are issued ahead of dQ of step t and the tensor cores never wait for
+// the elementwise work of the step they feed.  With both scores of step t + 1 ready early, a fast
+// warp can finish that step before a slow one has finished step t: the barrier the warps arrive on
+// when dS is written is therefore double as well (one per buffer).
+struct DqBarriers {
+    uint64_t res_full;
+    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t s_full, s_free, dp_full[2], ds_full[2];
+    uint64_t acc_ready;
+};
+
+struct DqTail {
+    DqBarriers bar;
+    uint32_t tmem_base;
+    unsigned int abort;
+    int red_lo[4 * KCG], red_hi[4 * KCG];
+};
+
+constexpr size_t DQ_TAIL = 1024;
+static_assert(sizeof(DqTail) <= DQ_TAIL, "the tail of the dq kernel's shared memory");
+// 1 KiB slack | Q, dO resident (2 x 32 KiB) | K ring 2 x 32 KiB | V ring 2 x 32 KiB | tail
+constexpr size_t SMEM_DQ = 1024 + 6 * BIG_BYTES + DQ_TAIL;
+constexpr int DQ_THREADS = 32 * (2 + 4 * KCG);
+
 template <typename T>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const Sm100BwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem, *do_s = q_s + BIG_BYTES;
-    uint8_t *k_s = do_s + BIG_BYTES;          // [2][STEP_BYTES]
-    uint8_t *v_s = k_s + 2 * STEP_BYTES;      // [2][STEP_BYTES]
-    uint8_t *ds_s = v_s + 2 * STEP_BYTES;     // [2][PS_BYTES]
-    SharedTail &sh = *reinterpret_cast<SharedTail *>(ds_s + 4 * PS_BYTES);
+    uint8_t *k_s = do_s + BIG_BYTES;          // [2][BIG_BYTES]
+    uint8_t *v_s = k_s + 2 * BIG_BYTES;       // [2][BIG_BYTES]
+    DqTail &sh = *reinterpret_cast<DqTail *>(v_s + 2 * BIG_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x;
@@ -630,14 +601,15 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
         mbar_init(BAR(sh.bar.res_full), 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(BAR(sh.bar.str_full[i]), 1);
-            mbar_init(BAR(sh.bar.str_empty[i]), 1);
-            mbar_init(BAR(sh.bar.aux_full[i]), 1);
-            mbar_init(BAR(sh.bar.sc_full[i]), 1);
-            mbar_init(BAR(sh.bar.sc_empty[i]), EW_THREADS);
-            mbar_init(BAR(sh.bar.ps_full[i]), EW_THREADS);
-            mbar_init(BAR(sh.bar.ps_empty[i]), 1);
+            mbar_init(BAR(sh.bar.k_full[i]), 1);
+            mbar_init(BAR(sh.bar.k_empty[i]), 1);
+            mbar_init(BAR(sh.bar.v_full[i]), 1);
+            mbar_init(BAR(sh.bar.v_empty[i]), 1);
+            mbar_init(BAR(sh.bar.dp_full[i]), 1);
+            mbar_init(BAR(sh.bar.ds_full[i]), 4 * KCG);
         }
+        mbar_init(BAR(sh.bar.s_full), 1);
+        mbar_init(BAR(sh.bar.s_free), 4 * KCG);    // one arrival per elementwise warp
         mbar_init(BAR(sh.bar.acc_ready), 1);
         fence_mbar_init();
         prefetch_tensormap(&tm_q);
@@ -656,7 +628,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (warp >= 2) {
         row_bounds(a.mask, m0 + r, a.tq, a.tk, lo, hi);
         int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
-        if (lane == 0 && sw < 4) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }  // one warp per lane quadrant
+        if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -665,11 +637,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const bool aborted = sh.abort != 0;
     int kmin = a.tk, kmax = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { kmin = min(kmin, sh.red_lo[i]); kmax = max(kmax, sh.red_hi[i]); }
-    const int steps = (!aborted && kmax > kmin) ? (kmax - kmin + STEP - 1) / STEP : 0;
+    for (int i = 0; i < 4; ++i) { kmin = min(kmin, sh.red_lo[i]); kmax = max(kmax, sh.red_hi[i]); }  // the first four warps cover every row
+    const int steps = (!aborted && kmax > kmin) ? (kmax - kmin + BIG - 1) / BIG : 0;
     bool failed = aborted;
-    // TMEM columns: S[2] at 0 / 64, dP[2] at 128 / 192, dQ at 256.
-    constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
+    // TMEM columns: S at 0, dP[2] at 128 / 256 (dS over the first half of every group of 32 columns), dQ at 384.
+    constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 384;
 
     if (warp == 0) {
         if (lane == 0 && steps > 0) {
@@ -680,72 +652,82 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tma_load_4d(smem_u32(do_s), &tm_do, full, 0, h, m0, b);
             tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
             for (int t = 0; t < steps; ++t) {
-                const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * STEP;
-                if (!mbar_wait(BAR(sh.bar.str_empty[st]), ph ^ 1)) { failed = true; break; }
-                const uint32_t sf = BAR(sh.bar.str_full[st]);
-                const uint32_t kd = smem_u32(k_s + st * STEP_BYTES), vd = smem_u32(v_s + st * STEP_BYTES);
-                mbar_expect_tx(sf, 2 * STEP_BYTES);
-                tma_load_4d(kd, &tm_k, sf, 0, hk, c0, b);
-                tma_load_4d(kd + STEP_HALF, &tm_k, sf, 64, hk, c0, b);
-                tma_load_4d(vd, &tm_v, sf, 0, hk, c0, b);
-                tma_load_4d(vd + STEP_HALF, &tm_v, sf, 64, hk, c0, b);
+                const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * BIG;
+                if (!mbar_wait(BAR(sh.bar.k_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t kf = BAR(sh.bar.k_full[st]), kd = smem_u32(k_s + st * BIG_BYTES);
+                mbar_expect_tx(kf, BIG_BYTES);
+                tma_load_4d(kd, &tm_k, kf, 0, hk, c0, b);
+                tma_load_4d(kd + BIG_HALF, &tm_k, kf, 64, hk, c0, b);
+                if (!mbar_wait(BAR(sh.bar.v_empty[st]), ph ^ 1)) { failed = true; break; }
+                const uint32_t vf = BAR(sh.bar.v_full[st]), vd = smem_u32(v_s + st * BIG_BYTES);
+                mbar_expect_tx(vf, BIG_BYTES);
+                tma_load_4d(vd, &tm_v, vf, 0, hk, c0, b);
+                tma_load_4d(vd + BIG_HALF, &tm_v, vf, 64, hk, c0, b);
             }
         }
     } else if (warp == 1) {
         // MMA issuer: the whole warp runs the loop, one elected lane issues.
         if (steps > 0) {
-            constexpr uint32_t IDESC_SC = idesc_f16(BIG, STEP, Pack<T>::FMT, 0, 0);   // [128 queries x 64 keys]
-            constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 queries x 128 d]
+            constexpr uint32_t IDESC_SC = idesc_f16(BIG, BIG, Pack<T>::FMT, 0, 0);    // [128 queries x 128 keys]
+            constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 queries x 128 d], B MN-major
             const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s), 16, 1024), g_desc = smem_desc_sw128(smem_u32(do_s), 16, 1024);
-            auto grads = [&](int i) -> bool {
-                const int st = i & 1, ph = (i >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_full[st]), ph))) return false;
+            auto a_cols = [](int ks) { return static_cast<uint32_t>(32 * (ks >> 1) + 8 * (ks & 1)); };
+            // S(t) = Q K^T once the elementwise threads have taken S(t - 1), and dP(t) = dO V^T into buffer t & 1.
+            auto scores = [&](int t) -> bool {
+                const int st = t & 1, ph = (t >> 1) & 1;
+                if (t > 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_free), (t - 1) & 1))) return false;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[st]), ph))) return false;
                 tc_fence_after_sync();
-                const uint64_t ds = smem_desc_sw128(smem_u32(ds_s + st * PS_BYTES), 16, 1024);
-                const uint64_t km = smem_desc_sw128(smem_u32(k_s + st * STEP_BYTES), STEP_HALF, 1024);
-                const uint32_t e0 = BAR(sh.bar.str_empty[st]), e1 = BAR(sh.bar.ps_empty[st]);
+                const uint64_t kk = smem_desc_sw128(smem_u32(k_s + st * BIG_BYTES), 16, 1024);
+                const uint32_t sf = BAR(sh.bar.s_full);
                 if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < STEP / 16; ++ks)   // dQ += dS K over 64 keys
-                        umma_f16(tmem + COL_DQ, desc_at(ds, ks * 32), desc_at(km, ks * 2048), IDESC_ACC, (i > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(e0);
-                    umma_commit(e1);
+                    for (int ks = 0; ks < HD / 16; ++ks)
+                        umma_f16(tmem + COL_S, desc_at(q_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(kk, (ks >> 2) * BIG_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    umma_commit(sf);
+                }
+                __syncwarp();
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full[st]), ph))) return false;
+                tc_fence_after_sync();
+                const uint64_t vk = smem_desc_sw128(smem_u32(v_s + st * BIG_BYTES), 16, 1024);
+                const uint32_t df = BAR(sh.bar.dp_full[st]), ve = BAR(sh.bar.v_empty[st]);
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ++ks)
+                        umma_f16(tmem + COL_DP + st * BIG, desc_at(g_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
+                                 desc_at(vk, (ks >> 2) * BIG_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
+                    umma_commit(df);
+                    umma_commit(ve);
                 }
                 __syncwarp();
                 return true;
             };
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.res_full), 0))) failed = true;
+            if (!failed && !scores(0)) failed = true;
             for (int t = 0; t < steps && !failed; ++t) {
-                const int st = t & 1, ph = (t >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.str_full[st]), ph) && mbar_wait(BAR(sh.bar.sc_empty[st]), ph ^ 1))) {
-                    failed = true;
-                    break;
-                }
+                const int st = t & 1;
+                if (t + 1 < steps && !scores(t + 1)) { failed = true; break; }
+                // dQ += dS K over the step's 128 keys; the K stage is free behind it.
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ds_full[st]), (t >> 1) & 1))) { failed = true; break; }
                 tc_fence_after_sync();
-                const uint64_t kk = smem_desc_sw128(smem_u32(k_s + st * STEP_BYTES), 16, 1024);
-                const uint64_t vk = smem_desc_sw128(smem_u32(v_s + st * STEP_BYTES), 16, 1024);
-                const uint32_t full = BAR(sh.bar.sc_full[st]);
+                const uint64_t km = smem_desc_sw128(smem_u32(k_s + st * BIG_BYTES), BIG_HALF, 1024);
+                const uint32_t ke = BAR(sh.bar.k_empty[st]);
                 if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks)   // S = Q K^T
-                        umma_f16(tmem + COL_S + st * STEP, desc_at(q_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                                 desc_at(kk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
-#pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks)   // dP = dO V^T
-                        umma_f16(tmem + COL_DP + st * STEP, desc_at(g_desc, (ks >> 2) * BIG_HALF + (ks & 3) * 32),
-                                 desc_at(vk, (ks >> 2) * STEP_HALF + (ks & 3) * 32), IDESC_SC, ks > 0 ? 1u : 0u);
-                    umma_commit(full);
+                    for (int ks = 0; ks < BIG / 16; ++ks)
+                        umma_f16_ts(tmem + COL_DQ, tmem + COL_DP + st * BIG + a_cols(ks), desc_at(km, ks * 2048), IDESC_ACC,
+                                    (t > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(ke);
                 }
                 __syncwarp();
-                if (t > 0 && !grads(t - 1)) { failed = true; break; }
             }
-            if (!failed && !grads(steps - 1)) failed = true;
             if (!failed && elect_one()) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
-        // ---------------- elementwise: a query row and CW of the step's columns per thread ----------------
+        // ---------------- elementwise: a query row and 32 of the step's keys per thread ----------------
         const int row = m0 + r;
-        const int cg = (warp - 2) >> 2, col0 = cg * CW;
+        const int cg = sw >> 2, col0 = cg * KQW;
         const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
         const bool padded = a.mask.kind == 1;
         float l2 = INFINITY, dl = 0.f;
@@ -756,43 +738,57 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             dl = a.delta[at];
         }
         for (int t = 0; t < steps && !failed; ++t) {
-            const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * STEP + col0;
+            const int st = t & 1, c0 = kmin + t * BIG + col0;
             uint32_t pb = 0;
             if (padded) {
                 const int key = c0 + lane;
                 pb = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.sc_full[st]), ph))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full), t & 1))) { failed = true; break; }
             tc_fence_after_sync();
-            float s[CW], dp[CW];
-            tmem_ld32(t_lane + COL_S + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld32(t_lane + COL_DP + st * STEP + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+            float p[KQW];
+            tmem_ld32(t_lane + COL_S + col0, *reinterpret_cast<uint32_t(*)[32]>(&p[0]));
             tmem_ld_wait();
             tc_fence_before_sync();
-            mbar_arrive(BAR(sh.bar.sc_empty[st]));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.s_free));
 
-            const bool clear = !padded && c0 >= lo && c0 + CW <= hi;
+            const bool clear = !padded && c0 >= lo && c0 + KQW <= hi;
             if (!__all_sync(0xffffffffu, clear)) {
 #pragma unroll
-                for (int c = 0; c < CW; ++c) {
+                for (int c = 0; c < KQW; ++c) {
                     const int key = c0 + c;
-                    s[c] = (key >= lo && key < hi && !((pb >> c) & 1u)) ? s[c] : -INFINITY;
+                    p[c] = (key >= lo && key < hi && !((pb >> c) & 1u)) ? p[c] : -INFINITY;
                 }
             }
 #pragma unroll
-            for (int c = 0; c < CW; ++c) {
-                const float p = ex2(fmaf(s[c], a.scale_log2, -l2));
-                dp[c] = p * (dp[c] - dl);
+            for (int c4 = 0; c4 < KQW / 4; ++c4) {
+                p[c4 * 4 + 0] = exp2_mixed<(POLY_OF4 > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2));
+                p[c4 * 4 + 1] = exp2_mixed<(POLY_OF4 > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2));
+                p[c4 * 4 + 2] = exp2_mixed<(POLY_OF4 > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2));
+                p[c4 * 4 + 3] = exp2_mixed<(POLY_OF4 > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2));
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ps_empty[st]), ph ^ 1))) { failed = true; break; }
-            store_row_cols<T>(ds_s + st * PS_BYTES, r, cg, dp);
-            fence_proxy_async_smem();
-            mbar_arrive(BAR(sh.bar.ps_full[st]));
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full[st]), (t >> 1) & 1))) { failed = true; break; }
+            tc_fence_after_sync();
+            {
+                float dp[KQW];
+                tmem_ld32(t_lane + COL_DP + st * BIG + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+                tmem_ld_wait();
+                uint32_t ds[KQW / 2];
+#pragma unroll
+                for (int c2 = 0; c2 < KQW / 2; ++c2)
+                    ds[c2] = Pack<T>::two(p[2 * c2] * (dp[2 * c2] - dl), p[2 * c2 + 1] * (dp[2 * c2 + 1] - dl));
+                tmem_st16(t_lane + COL_DP + st * BIG + col0, ds);   // over the first half of the f32 columns just read
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full[st]));
         }
-        constexpr int EC = HD / CG;
+        constexpr int EC = HD / KCG;
         T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + cg * EC;
         if (steps == 0 || failed) {
-            if (row < a.tq && !failed) store_zero_cols(dq);
+            if (row < a.tq && !failed) store_zero_cols<T, 16 / KCG>(dq);
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             tc_fence_after_sync();
             store_acc_cols<T>(t_lane + COL_DQ + cg * EC, dq, a.scale, row < a.tq, EC / 32);
@@ -816,10 +812,10 @@ template <typename T>
 static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t stream, int *launches) {
     cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DKDV);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DQ);
     if (e != cudaSuccess) return e;
     dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
-    bwd_dq_sm100_kernel<T><<<gq, THREADS, SMEM_BYTES, stream>>>(m.q128, m.do128, m.k64, m.v64, a);
+    bwd_dq_sm100_kernel<T><<<gq, DQ_THREADS, SMEM_DQ, stream>>>(m.q128, m.do128, m.k128, m.v128, a);
     *launches += 1;
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);
