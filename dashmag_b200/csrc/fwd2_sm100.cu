@@ -7,20 +7,23 @@
 // runs two softmax warpgroups, one per tile, so that every scheduler has two warps of elementwise
 // work to interleave.  352 threads:
 //   warp 0, 10  one lane each issues the TMA tile loads: warp 0 both Q tiles once and then the K
-//               tiles of 64 keys, warp 10 the V tiles, into three-stage rings of 128-byte-swizzled
+//               tiles of 128 keys, warp 10 the V tiles, into two-stage rings of 128-byte-swizzled
 //               shared memory;
-//   warp 1      owns tensor memory (512 columns: per tile two S buffers of 64 columns and the
+//   warp 1      owns tensor memory (512 columns: per tile the 128-column S buffer and the
 //               128-column O accumulator) and issues the tcgen05 MMAs from warp-uniform code under
-//               an elected lane: S_t = Q_t K_j^T for both tiles, then O_t += P_t V_j of the step
-//               before;
+//               an elected lane, every one 128 x 128 x 16 (the width at which the tensor cores
+//               run at full rate): O_t += P_t V of the step before, then S_t = Q_t K_j^T, tile by
+//               tile;
 //   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one query row per thread (TMEM lane =
 //               row): read S from tensor memory, mask what the row does not see, keep the online
 //               softmax in f32 with the scale folded into an exp2, write P rounded to the input
-//               dtype into shared memory in the layout of an MMA A operand, and at the end
-//               normalise O and store it with the row's log-sum-exp.
-// S and P are double per tile, so the products of one step run under the softmax of its neighbours
-// and of the other tile.  Lazy row maximum, masking, bounded waits and the status word as in the
-// one-tile kernel (fwd_sm100.cu), which stays for head dimensions and shapes this one leaves.
+//               dtype back into tensor memory over the first half of the S columns (two 16-bit
+//               values per 32-bit column: the A operand of P V comes from tensor memory), and at
+//               the end normalise O and store it with the row's log-sum-exp.
+// S is single per tile: S_t of the next step is issued right behind P_t V of this one (MMAs of one
+// thread execute in issue order), and runs - with the other tile's products - under the other
+// tile's softmax.  Lazy row maximum, masking, bounded waits and the status word as in the one-tile
+// kernel (fwd_sm100.cu), which stays for comparison runs.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -37,22 +40,21 @@ __device__ unsigned int g_sm100_fwd2_status = 0;  // sticky: non-zero once a bou
 namespace {
 
 constexpr int BM = 128;                   // queries per tile
-constexpr int BN = 64;                    // keys per step
+constexpr int BN = 128;                   // keys per step
 constexpr int HD = 128;
 constexpr int NT = 2;                     // query tiles per block
-constexpr int NS = 3;                     // stages of the K and of the V ring
+constexpr int NS = 2;                     // stages of the K and of the V ring
 constexpr int Q_BYTES = BM * HD * 2;      // 32 KiB per tile
 constexpr int Q_HALF = Q_BYTES / 2;       // 128 rows of 128 bytes
-constexpr int KV_BYTES = BN * HD * 2;     // 16 KiB
-constexpr int KV_HALF = KV_BYTES / 2;     // 64 rows of 128 bytes
-constexpr int P_BYTES = BM * BN * 2;      // 16 KiB: 128 rows of 128 bytes
+constexpr int KV_BYTES = BN * HD * 2;     // 32 KiB
+constexpr int KV_HALF = KV_BYTES / 2;     // 128 rows of 128 bytes
 constexpr int THREADS = 352;
 constexpr int V_WARP = 10;
 constexpr float RESCALE_LOG2 = 8.0f;
 
 struct Barriers {
     uint64_t q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
-    uint64_t s_full[NT][2], s_empty[NT][2], p_full[NT][2], p_empty[NT][2], o_ready[NT];
+    uint64_t s_full[NT], p_full[NT], o_ready[NT];
 };
 
 struct Shared {
@@ -60,10 +62,11 @@ struct Shared {
     uint32_t tmem_base;
     int red_lo[4 * NT], red_hi[4 * NT];
     unsigned int abort;
+    int tile_bad[NT];   // a softmax warp of the tile gave up: its output is not stored
 };
 
-// 1 KiB slack | Q x 2 | K ring | V ring | P [tile][buffer] | Shared
-constexpr size_t SMEM_BYTES = 1024 + NT * Q_BYTES + 2 * NS * KV_BYTES + NT * 2 * P_BYTES + 1024;
+// 1 KiB slack | Q x 2 | K ring | V ring | Shared
+constexpr size_t SMEM_BYTES = 1024 + NT * Q_BYTES + 2 * NS * KV_BYTES + 1024;
 
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
@@ -86,14 +89,13 @@ template <> struct Pack<__half> {
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 1)
 fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const Sm100FwdArgs a) {
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Sm100FwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem;                       // [NT][Q_BYTES]
     uint8_t *k_s = q_s + NT * Q_BYTES;         // [NS][KV_BYTES]
     uint8_t *v_s = k_s + NS * KV_BYTES;        // [NS][KV_BYTES]
-    uint8_t *p_s = v_s + NS * KV_BYTES;        // [NT][2][P_BYTES]
-    Shared &sh = *reinterpret_cast<Shared *>(p_s + NT * 2 * P_BYTES);
+    Shared &sh = *reinterpret_cast<Shared *>(v_s + NS * KV_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qt = gridDim.y - 1 - blockIdx.y;  // later (longer, under causality) tiles first
@@ -109,6 +111,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_fwd2_status);
+        sh.tile_bad[0] = sh.tile_bad[1] = 0;
         mbar_init(BAR(sh.bar.q_full), 1);
         for (int i = 0; i < NS; ++i) {
             mbar_init(BAR(sh.bar.k_full[i]), 1);
@@ -117,18 +120,25 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(BAR(sh.bar.v_empty[i]), 1);
         }
         for (int t = 0; t < NT; ++t) {
-            for (int i = 0; i < 2; ++i) {
-                mbar_init(BAR(sh.bar.s_full[t][i]), 1);
-                mbar_init(BAR(sh.bar.s_empty[t][i]), 128);
-                mbar_init(BAR(sh.bar.p_full[t][i]), 128);
-                mbar_init(BAR(sh.bar.p_empty[t][i]), 1);
-            }
+            mbar_init(BAR(sh.bar.s_full[t]), 1);
+            mbar_init(BAR(sh.bar.p_full[t]), 4);   // one arrival per softmax warp
             mbar_init(BAR(sh.bar.o_ready[t]), 1);
         }
         fence_mbar_init();
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_o);
+        // Both Q tiles are on their way before the block knows which keys it sweeps: their flight
+        // covers the rest of the setup.  (A block that turns out to have nothing to do waits for
+        // them at the end: shared memory must not be written behind a block that has left.)
+        const uint32_t qf = BAR(sh.bar.q_full);
+        mbar_expect_tx(qf, NT * Q_BYTES);
+        for (int t = 0; t < NT; ++t) {
+            const uint32_t dst = smem_u32(q_s + t * Q_BYTES);
+            tma_load_4d(dst, &tm_q, qf, 0, tile_head(t), tile_row0(t), b);
+            tma_load_4d(dst + Q_HALF, &tm_q, qf, 64, tile_head(t), tile_row0(t), b);
+        }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -157,20 +167,13 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const bool aborted = sh.abort != 0;
     const int steps = (!aborted && kmax > kmin) ? (kmax - kmin + BN - 1) / BN : 0;
     bool failed = aborted;
-    // TMEM columns: S[tile][buffer] at (2 tile + buffer) * 64, O[tile] at 256 + 128 tile.
-    auto COL_S = [](int t, int buf) { return static_cast<uint32_t>((2 * t + buf) * BN); };
+    // TMEM columns: S[tile] at 128 tile (P over its first 64 columns), O[tile] at 256 + 128 tile.
+    auto COL_S = [](int t) { return static_cast<uint32_t>(t * BN); };
     auto COL_O = [](int t) { return static_cast<uint32_t>(256 + t * HD); };
 
     if (warp == 0) {
-        // ---------------- TMA producer: both Q tiles, then the K ring ----------------
+        // ---------------- TMA producer of the K ring (the Q tiles were issued during the setup) ----------------
         if (lane == 0 && steps > 0) {
-            const uint32_t qf = BAR(sh.bar.q_full);
-            mbar_expect_tx(qf, NT * Q_BYTES);
-            for (int t = 0; t < NT; ++t) {
-                const uint32_t dst = smem_u32(q_s + t * Q_BYTES);
-                tma_load_4d(dst, &tm_q, qf, 0, tile_head(t), tile_row0(t), b);
-                tma_load_4d(dst + Q_HALF, &tm_q, qf, 64, tile_head(t), tile_row0(t), b);
-            }
             for (int j = 0; j < steps; ++j) {
                 const int st = j % NS, ph = (j / NS) & 1, k0 = kmin + j * BN;
                 if (!mbar_wait(BAR(sh.bar.k_empty[st]), ph ^ 1)) { failed = true; break; }
@@ -195,60 +198,58 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
         if (steps > 0) {
-            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, Pack<T>::FMT, 0, 0);   // [128 q x 64 keys], A = Q, B = K K-major
-            constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // [128 q x 128 d], A = P, B = V MN-major
+            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, Pack<T>::FMT, 0, 0);   // [128 q x 128 keys], A = Q, B = K K-major
+            constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // [128 q x 128 d], A = P (TMEM), B = V MN-major
             uint64_t q_desc[NT];
 #pragma unroll
             for (int t = 0; t < NT; ++t) q_desc[t] = smem_desc_sw128(smem_u32(q_s + t * Q_BYTES), 16, 1024);
-            // O_t += P_t V of step i, for both tiles; V's stage is released after the second.
-            auto issue_pv = [&](int i) -> bool {
-                const int st = i % NS, vph = (i / NS) & 1, pb = i & 1, pph = (i >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full[st]), vph))) return false;
+            // S_t(j) = Q_t K_j^T; the K stage is released behind the second tile's.
+            auto issue_s = [&](int j, int t) -> bool {
+                const int st = j % NS, kph = (j / NS) & 1;
+                if (t == 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[st]), kph))) return false;
+                tc_fence_after_sync();
+                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + st * KV_BYTES), 16, 1024);
+                const uint32_t sf = BAR(sh.bar.s_full[t]), ke = BAR(sh.bar.k_empty[st]);
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ++ks)
+                        umma_f16(tmem + COL_S(t), desc_at(q_desc[t], (ks >> 2) * Q_HALF + (ks & 3) * 32),
+                                 desc_at(k_desc, (ks >> 2) * KV_HALF + (ks & 3) * 32), IDESC_S, ks > 0 ? 1u : 0u);
+                    umma_commit(sf);
+                    if (t == NT - 1) umma_commit(ke);
+                }
+                __syncwarp();
+                return true;
+            };
+            // O_t += P_t(i) V_i with P read from the S columns of the tile; the V stage is released
+            // behind the second tile's.
+            auto issue_pv = [&](int i, int t) -> bool {
+                const int st = i % NS, vph = (i / NS) & 1;
+                if (t == 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full[st]), vph))) return false;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[t]), i & 1))) return false;
+                tc_fence_after_sync();
                 // V rows are keys (the K of this product): 64-column halves KV_HALF apart, 8-key groups 1024 B apart.
                 const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * KV_BYTES), KV_HALF, 1024);
+                const uint32_t orr = BAR(sh.bar.o_ready[t]), ve = BAR(sh.bar.v_empty[st]);
+                if (elect_one()) {
 #pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[t][pb]), pph))) return false;
-                    tc_fence_after_sync();
-                    const uint64_t p_desc = smem_desc_sw128(smem_u32(p_s + (t * 2 + pb) * P_BYTES), 16, 1024);
-                    const uint32_t pe = BAR(sh.bar.p_empty[t][pb]), orr = BAR(sh.bar.o_ready[t]), ve = BAR(sh.bar.v_empty[st]);
-                    if (elect_one()) {
-#pragma unroll
-                        for (int ks = 0; ks < BN / 16; ++ks)
-                            umma_f16(tmem + COL_O(t), desc_at(p_desc, ks * 32), desc_at(v_desc, ks * 2048), IDESC_O,
-                                     (i > 0 || ks > 0) ? 1u : 0u);
-                        umma_commit(pe);
-                        umma_commit(orr);
-                        if (t == NT - 1) umma_commit(ve);
-                    }
-                    __syncwarp();
+                    for (int ks = 0; ks < BN / 16; ++ks)
+                        umma_f16_ts(tmem + COL_O(t), tmem + COL_S(t) + ks * 8, desc_at(v_desc, ks * 2048), IDESC_O,
+                                    (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(orr);
+                    if (t == NT - 1) umma_commit(ve);
                 }
+                __syncwarp();
                 return true;
             };
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_full), 0))) failed = true;
-            for (int j = 0; j < steps && !failed; ++j) {
-                const int st = j % NS, kph = (j / NS) & 1, sb = j & 1, sph = (j >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[st]), kph))) { failed = true; break; }
-                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + st * KV_BYTES), 16, 1024);
+            if (!failed && !(issue_s(0, 0) && issue_s(0, 1))) failed = true;
+            for (int j = 1; j < steps && !failed; ++j) {
 #pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_empty[t][sb]), sph ^ 1))) { failed = true; break; }
-                    tc_fence_after_sync();
-                    const uint32_t sf = BAR(sh.bar.s_full[t][sb]), ke = BAR(sh.bar.k_empty[st]);
-                    if (elect_one()) {
-#pragma unroll
-                        for (int ks = 0; ks < HD / 16; ++ks)
-                            umma_f16(tmem + COL_S(t, sb), desc_at(q_desc[t], (ks >> 2) * Q_HALF + (ks & 3) * 32),
-                                     desc_at(k_desc, (ks >> 2) * KV_HALF + (ks & 3) * 32), IDESC_S, ks > 0 ? 1u : 0u);
-                        umma_commit(sf);
-                        if (t == NT - 1) umma_commit(ke);
-                    }
-                    __syncwarp();
-                }
-                if (failed) break;
-                if (j > 0 && !issue_pv(j - 1)) { failed = true; break; }
+                for (int t = 0; t < NT; ++t)
+                    if (!(issue_pv(j - 1, t) && issue_s(j, t))) { failed = true; break; }
             }
-            if (!failed && !issue_pv(steps - 1)) failed = true;
+            if (!failed && !(issue_pv(steps - 1, 0) && issue_pv(steps - 1, 1))) failed = true;
         }
     } else {
         // ---------------- softmax of one tile, one row per thread ----------------
@@ -259,23 +260,21 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float2 sl2 = make_float2(a.scale_log2, a.scale_log2);
         float m_ref = -INFINITY, l = 0.f;
         for (int j = 0; j < steps && !failed; ++j) {
-            const int sb = j & 1, sph = (j >> 1) & 1, k0 = kmin + j * BN;
-            uint32_t pb[2] = {0, 0};
+            const int k0 = kmin + j * BN;
+            uint32_t pb[BN / 32] = {0, 0, 0, 0};
             if (padded) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
+                for (int i = 0; i < BN / 32; ++i) {
                     const int key = k0 + i * 32 + lane;
                     pb[i] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
                 }
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full[t][sb]), sph))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full[t]), j & 1))) { failed = true; break; }
             tc_fence_after_sync();
             float s[BN];
-            tmem_ld32(t_lane + COL_S(t, sb), *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-            tmem_ld32(t_lane + COL_S(t, sb) + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) tmem_ld32(t_lane + COL_S(t) + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             tmem_ld_wait();
-            tc_fence_before_sync();
-            mbar_arrive(BAR(sh.bar.s_empty[t][sb]));
 
             const bool clear = !padded && k0 >= lo && k0 + BN <= hi;  // the row sees the whole step
             if (!__all_sync(0xffffffffu, clear)) {
@@ -310,24 +309,19 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float neg = m_ref == -INFINITY ? 0.f : -m_ref * a.scale_log2;
             const float2 neg2 = make_float2(neg, neg);
 
-            // The P buffer is free once P V of step j - 2 has completed.
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_empty[t][sb]), sph ^ 1))) { failed = true; break; }
-            uint8_t *p_row = p_s + (t * 2 + sb) * P_BYTES + r * 128;
+            // P over the first 64 of the S columns this thread has read, 32 keys (16 columns) at a time.
             float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int cc = 0; cc < BN / 8; ++cc) {
-                float p[8];
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t pk[16];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 x = fma2(make_float2(s[cc * 8 + 2 * e], s[cc * 8 + 2 * e + 1]), sl2, neg2);
-                    p[2 * e] = ex2(x.x);
-                    p[2 * e + 1] = ex2(x.y);
-                    sum2[e] = add2(sum2[e], make_float2(p[2 * e], p[2 * e + 1]));
+                for (int e = 0; e < 16; ++e) {
+                    const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
+                    const float p0 = ex2(x.x), p1 = ex2(x.y);
+                    sum2[e & 3] = add2(sum2[e & 3], make_float2(p0, p1));
+                    pk[e] = Pack<T>::two(p0, p1);
                 }
-                uint4 v = make_uint4(Pack<T>::two(p[0], p[1]), Pack<T>::two(p[2], p[3]), Pack<T>::two(p[4], p[5]),
-                                     Pack<T>::two(p[6], p[7]));
-                // 16-byte chunk cc of the row's 128 bytes, XOR-swizzled by the row.
-                *reinterpret_cast<uint4 *>(p_row + ((cc ^ (r & 7)) << 4)) = v;
+                tmem_st16(t_lane + COL_S(t) + cc * 16, pk);
             }
             {
                 const float2 tsum = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
@@ -347,12 +341,12 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
                         tmem_st32(t_lane + COL_O(t) + c * 32, o);
                     }
-                    tmem_st_wait();
-                    tc_fence_before_sync();
                 }
             }
-            fence_proxy_async_smem();
-            mbar_arrive(BAR(sh.bar.p_full[t][sb]));
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[t]));
         }
 
         // ---------------- epilogue ----------------
@@ -366,23 +360,28 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 a.lse[base] = -INFINITY;
             }
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (steps - 1) & 1))) {
+            // Every MMA has completed, so the tile's Q is dead: the normalised rows are staged over
+            // it in the layout of the TMA box (two halves of 64 columns, 128-byte rows, 16-byte
+            // chunks XOR-swizzled by the row) and leave as two bulk stores - whole lines instead of
+            // 16 bytes per thread and row - which also drop the rows past the last query.
             tc_fence_after_sync();
             const float inv = l > 0.f ? 1.f / l : 0.f;
+            uint8_t *stage = q_s + t * Q_BYTES;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t o[32];
                 tmem_ld32(t_lane + COL_O(t) + c * 32, o);
                 tmem_ld_wait();
-                if (row < a.tq) {
+                uint8_t *half_row = stage + (c >> 1) * Q_HALF + r * 128;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint4 v;
-                        v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
-                        v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
-                        v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
-                        v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
-                        reinterpret_cast<uint4 *>(out + base * HD)[c * 4 + e] = v;
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    uint4 v;
+                    v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * inv, __uint_as_float(o[8 * e + 1]) * inv);
+                    v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * inv, __uint_as_float(o[8 * e + 3]) * inv);
+                    v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * inv, __uint_as_float(o[8 * e + 5]) * inv);
+                    v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * inv, __uint_as_float(o[8 * e + 7]) * inv);
+                    const int chunk = (c & 1) * 4 + e;   // 16-byte chunk of the half row
+                    *reinterpret_cast<uint4 *>(half_row + ((chunk ^ (r & 7)) << 4)) = v;
                 }
             }
             if (row < a.tq) a.lse[base] = l > 0.f ? m_ref * a.scale + logf(l) : -INFINITY;
@@ -390,8 +389,23 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         } else {
             failed = true;
         }
+        if (steps > 0) {
+            // Every warp of the tile gets here (all waits are bounded), whatever became of it: one
+            // that gave up marks the tile, and nothing is stored from a tile that is not whole.
+            if (failed && lane == 0) sh.tile_bad[t] = 1;
+            fence_proxy_async_smem();
+            named_barrier(1 + t, 128);   // the tile's four warps
+            if ((warp & 3) == 2 && lane == 0 && sh.tile_bad[t] == 0) {
+                uint8_t *stage = q_s + t * Q_BYTES;
+                tma_store_4d(&tm_o, smem_u32(stage), 0, h, tile_row0(t), b);
+                tma_store_4d(&tm_o, smem_u32(stage + Q_HALF), 64, h, tile_row0(t), b);
+                tma_store_commit();
+                tma_store_wait_read();
+            }
+        }
     }
 
+    if (threadIdx.x == 0 && steps == 0 && !mbar_wait(BAR(sh.bar.q_full), 0)) failed = true;
     if (failed && !aborted) atomicOr(&g_sm100_fwd2_status, 8u);
     // Teardown: every thread gets here (all waits are bounded); the allocating warp frees TMEM.
     tc_fence_before_sync();
@@ -403,17 +417,17 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }
 
 cudaError_t launch_fwd2_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
-                              const Sm100FwdArgs &a, cudaStream_t stream) {
+                              const CUtensorMap &to, const Sm100FwdArgs &a, cudaStream_t stream) {
     dim3 grid(a.pair_heads ? a.hq / 2 : a.hq, a.pair_heads ? (a.tq + BM - 1) / BM : (a.tq + NT * BM - 1) / (NT * BM), a.b);
     cudaError_t e;
     if (dtype == DASH_ATTN_BF16) {
         e = cudaFuncSetAttribute(fwd2_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        fwd2_sm100_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
+        fwd2_sm100_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, to, a);
     } else {
         e = cudaFuncSetAttribute(fwd2_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        fwd2_sm100_kernel<__half><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
+        fwd2_sm100_kernel<__half><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, to, a);
     }
     return cudaGetLastError();
 }

@@ -110,9 +110,12 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     // The two-tile kernel shares every K / V tile between two query tiles; DASH_ATTN_FWD_TILES=1
     // keeps the one-tile kernel (for comparison runs).
     static const bool one_tile = [] { const char *e = std::getenv("DASH_ATTN_FWD_TILES"); return e && std::atoi(e) == 1; }();
-    const int kv_rows = one_tile ? 128 : 64;
-    CUtensorMap tq, tk, tv;
-    if (!encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride, 128) ||
+    const int kv_rows = 128;
+    (void)one_tile;
+    CUtensorMap tq, tk, tv, to;
+    const int64_t o_stride[4] = {(int64_t)p->tq * p->hq * 128, (int64_t)p->hq * 128, 128, 1};   // the output is contiguous
+    if (!encode(&to, p->dtype, a.out, p->b, p->tq, p->hq, o_stride, 128) ||
+        !encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride, 128) ||
         !encode(&tk, p->dtype, a.k.ptr, p->b, p->tk, p->hkv, p->k_stride, kv_rows) ||
         !encode(&tv, p->dtype, a.v.ptr, p->b, p->tk, p->hkv, p->v_stride, kv_rows)) {
         err = "attention: the driver refused a TMA tensor map over the inputs";
@@ -126,7 +129,7 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     f.lse = a.lse;
     f.mask = a.mask;
     f.pair_heads = ((p->hq / p->hkv) % 2 == 0) ? 1 : 0;
-    cudaError_t e = one_tile ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, f, stream);
+    cudaError_t e = one_tile ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, to, f, stream);
     *launches += 1;
     return e;
 }

@@ -43,7 +43,7 @@ cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap
                              const Sm100FwdArgs &a, cudaStream_t stream);
 // The two-tile forward: tq with boxes of 128 rows, tk / tv with boxes of 64 rows.
 cudaError_t launch_fwd2_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
-                              const Sm100FwdArgs &a, cudaStream_t stream);
+                              const CUtensorMap &to, const Sm100FwdArgs &a, cudaStream_t stream);
 cudaError_t read_sm100_fwd2_status(unsigned int *status, bool clear);
 // Reads (and optionally clears) the sticky device word the kernels raise when a bounded wait ran
 // out.  Synchronises with the device.
