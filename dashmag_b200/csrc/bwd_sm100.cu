@@ -333,9 +333,16 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             }
         };
         if (steps > 0) gather(0);
+        // The sequence of the step's first row: searched for at the start of a head's sweep, walked
+        // forward from there (the sweep's rows only grow).
+        int seq0 = 0;
         for (int t = 0; t < steps; ++t) {
             const int st = t & 1, ph = (t >> 1) & 1;
             const int q0 = qfirst + (t % tiles) * QS;
+            if (qmask.kind == 2) {
+                if (t % tiles == 0) seq0 = sequence_of(qmask.cu_q, qmask.idx_bytes, qmask.seqs, q0);
+                else while (seq0 + 1 <= qmask.seqs && load_index(qmask.cu_q, qmask.idx_bytes, seq0 + 1) <= q0) ++seq0;
+            }
             float lse_c[RPL], dl_c[RPL];
 #pragma unroll
             for (int i = 0; i < RPL; ++i) { lse_c[i] = lse_n[i]; dl_c[i] = dl_n[i]; }
@@ -349,7 +356,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 const bool in = q < a.tq;
                 l2v[i] = (!in || lse_c[i] == -INFINITY) ? INFINITY : lse_c[i] * LOG2E;
                 dlv[i] = in ? dl_c[i] : 0.f;
-                row_bounds(qmask, q, a.tq, a.tk, lov[i], hiv[i]);
+                int seq = seq0;   // this row's sequence: at or after the step's first row's
+                row_bounds_from(qmask, seq, q, a.tq, a.tk, lov[i], hiv[i]);
                 clear = clear && lov[i] <= k0 && hiv[i] >= k0 + BIG;
             }
             // aux[st] is free when the Q stage is: the elementwise threads of step t - 2 are done with it.

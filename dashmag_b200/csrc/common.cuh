@@ -77,21 +77,45 @@ __device__ __forceinline__ int sequence_of(const void *cu, int bytes, int seqs, 
     return lo - 1;
 }
 
+// The keys query `row` of packed sequence `s` sees, [lo, hi), or (tk, 0) when it sees none.
+__device__ __forceinline__ void row_bounds_in_sequence(const MaskArgs &m, int s, int row, int tk, int &lo, int &hi) {
+    lo = tk;
+    hi = 0;
+    if (s < 0 || s >= m.seqs) return;
+    int q0 = load_index(m.cu_q, m.idx_bytes, s), q1 = load_index(m.cu_q, m.idx_bytes, s + 1);
+    int k0 = load_index(m.cu_k, m.idx_bytes, s), k1 = load_index(m.cu_k, m.idx_bytes, s + 1);
+    int lk = k1 - k0, lq = q1 - q0;
+    int pos = row - q0 + lk - lq;
+    int a = max(k0 + max(0, pos - m.left), 0);
+    int c = min(k0 + min(lk, pos + m.right + 1), tk);
+    if (c > a) { lo = a; hi = c; }
+}
+
 // The keys query `row` sees, [lo, hi), or (tk, 0) when it sees none or lies past the queries.
 __device__ __forceinline__ void row_bounds(const MaskArgs &m, int row, int tq, int tk, int &lo, int &hi) {
     lo = tk;
     hi = 0;
     if (row < 0 || row >= tq) return;
     if (m.kind == 2) {
-        int s = sequence_of(m.cu_q, m.idx_bytes, m.seqs, row);
-        if (s < 0 || s >= m.seqs) return;
-        int q0 = load_index(m.cu_q, m.idx_bytes, s), q1 = load_index(m.cu_q, m.idx_bytes, s + 1);
-        int k0 = load_index(m.cu_k, m.idx_bytes, s), k1 = load_index(m.cu_k, m.idx_bytes, s + 1);
-        int lk = k1 - k0, lq = q1 - q0;
-        int pos = row - q0 + lk - lq;
-        int a = max(k0 + max(0, pos - m.left), 0);
-        int c = min(k0 + min(lk, pos + m.right + 1), tk);
+        row_bounds_in_sequence(m, sequence_of(m.cu_q, m.idx_bytes, m.seqs, row), row, tk, lo, hi);
+    } else {
+        int pos = row + tk - tq;
+        int a = max(0, pos - m.left);
+        int c = min(tk, pos + m.right + 1);
         if (c > a) { lo = a; hi = c; }
+    }
+}
+
+// The same for a query at or after one whose sequence is known: `s` is the sequence of an earlier
+// row (what sequence_of gave for it) and is walked forward to this row's, a step or two instead of
+// a search when consecutive tiles of rows are asked for in turn.
+__device__ __forceinline__ void row_bounds_from(const MaskArgs &m, int &s, int row, int tq, int tk, int &lo, int &hi) {
+    lo = tk;
+    hi = 0;
+    if (row < 0 || row >= tq) return;
+    if (m.kind == 2) {
+        while (s + 1 <= m.seqs && load_index(m.cu_q, m.idx_bytes, s + 1) <= row) ++s;
+        row_bounds_in_sequence(m, s, row, tk, lo, hi);
     } else {
         int pos = row + tk - tq;
         int a = max(0, pos - m.left);
