@@ -137,6 +137,32 @@ __device__ __forceinline__ void query_range(const MaskArgs &m, int k0, int k1, i
     if (end < first) end = first;
 }
 
+// The queries [first, end) that see key `key`: the inverse of the visible interval (both ends of a
+// query's interval grow with the query, so the queries that see one key are an interval as well),
+// from the same closed form as query_range and exact.  Key padding is the caller's to apply.
+__device__ __forceinline__ void queries_of_key(const MaskArgs &m, int key, int tq, int tk, int &first, int &end) {
+    first = 0;
+    end = 0;
+    if (key < 0 || key >= tk) return;
+    if (m.kind == 2) {
+        const int s = sequence_of(m.cu_k, m.idx_bytes, m.seqs, key);
+        if (s < 0 || s >= m.seqs) return;
+        const int q0 = load_index(m.cu_q, m.idx_bytes, s), q1 = load_index(m.cu_q, m.idx_bytes, s + 1);
+        const int k0 = load_index(m.cu_k, m.idx_bytes, s), k1 = load_index(m.cu_k, m.idx_bytes, s + 1);
+        if (key >= k1) return;   // between sequences
+        const int off = (k1 - k0) - (q1 - q0), rel = key - k0;
+        first = max(q0, q0 + rel - m.right - off);
+        end = min(q1, q0 + rel + m.left - off + 1);
+    } else {
+        const int off = tk - tq;
+        first = max(0, key - m.right - off);
+        end = min(tq, key + m.left - off + 1);
+    }
+    first = max(first, 0);
+    end = min(end, tq);
+    if (end < first) end = first;
+}
+
 constexpr int CU_CACHE = 768;   // offsets of packed sequences kept in shared memory (dkdv)
 
 }  // namespace
@@ -200,8 +226,6 @@ struct DkdvBarriers {
 struct alignas(16) QAux {   // what the elementwise threads need per query of a step
     float lse2[QS];        // log-sum-exp in base 2, +inf for a query that saw no key or is out of range
     float delta[QS];
-    int lo[QS], hi[QS];
-    int clear;             // every query of the step sees every key of the block
 };
 
 struct DkdvTail {
@@ -333,32 +357,19 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             }
         };
         if (steps > 0) gather(0);
-        // The sequence of the step's first row: searched for at the start of a head's sweep, walked
-        // forward from there (the sweep's rows only grow).
-        int seq0 = 0;
         for (int t = 0; t < steps; ++t) {
             const int st = t & 1, ph = (t >> 1) & 1;
             const int q0 = qfirst + (t % tiles) * QS;
-            if (qmask.kind == 2) {
-                if (t % tiles == 0) seq0 = sequence_of(qmask.cu_q, qmask.idx_bytes, qmask.seqs, q0);
-                else while (seq0 + 1 <= qmask.seqs && load_index(qmask.cu_q, qmask.idx_bytes, seq0 + 1) <= q0) ++seq0;
-            }
             float lse_c[RPL], dl_c[RPL];
 #pragma unroll
             for (int i = 0; i < RPL; ++i) { lse_c[i] = lse_n[i]; dl_c[i] = dl_n[i]; }
             if (t + 1 < steps) gather(t + 1);
             float l2v[RPL], dlv[RPL];
-            int lov[RPL], hiv[RPL];
-            bool clear = true;
 #pragma unroll
             for (int i = 0; i < RPL; ++i) {
-                const int q = q0 + lane + 32 * i;
-                const bool in = q < a.tq;
+                const bool in = q0 + lane + 32 * i < a.tq;
                 l2v[i] = (!in || lse_c[i] == -INFINITY) ? INFINITY : lse_c[i] * LOG2E;
                 dlv[i] = in ? dl_c[i] : 0.f;
-                int seq = seq0;   // this row's sequence: at or after the step's first row's
-                row_bounds_from(qmask, seq, q, a.tq, a.tk, lov[i], hiv[i]);
-                clear = clear && lov[i] <= k0 && hiv[i] >= k0 + BIG;
             }
             // aux[st] is free when the Q stage is: the elementwise threads of step t - 2 are done with it.
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_empty[st]), ph ^ 1))) { failed = true; break; }
@@ -368,11 +379,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 const int c = lane + 32 * i;
                 aux.lse2[c] = l2v[i];
                 aux.delta[c] = dlv[i];
-                aux.lo[c] = lov[i];
-                aux.hi[c] = hiv[i];
             }
-            clear = __all_sync(0xffffffffu, clear) && a.mask.kind != 1;
-            if (lane == 0) aux.clear = clear ? 1 : 0;
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(sh.bar.aux_full[st]));
         }
@@ -462,9 +469,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const int r = lane_base + lane;
         const int key = k0 + r;
         const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
-        const bool open = key < a.tk && !key_padded(a.mask, b, key);
+        // The queries that see this thread's key: one interval for the whole sweep (empty for a
+        // padded key), so a step needs masking only where its columns leave that interval.
+        int qa = 0, qb = 0;
+        if (key < a.tk && !key_padded(a.mask, b, key)) queries_of_key(qmask, key, a.tq, a.tk, qa, qb);
         for (int t = 0; t < steps && !failed; ++t) {
             const int st = t & 1, aph = (t >> 1) & 1, ph = t & 1;
+            const int c0 = qfirst + (t % tiles) * QS + col0;   // the first query of this thread's columns
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.aux_full[st]), aph) && mbar_wait(BAR(sh.bar.s_full), ph))) {
                 failed = true;
                 break;
@@ -474,13 +485,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             tmem_ld32(t_lane + COL_ST + col0, *reinterpret_cast<uint32_t(*)[32]>(&p[0]));
             tmem_ld_wait();
             const QAux &aux = sh.aux[st];
-            if (aux.clear == 0) {
-                // A step that cuts some query's interval (or has padded keys): hide what this key
-                // is not seen by before the exponentials, in a pass of its own so that the common,
+            if (!__all_sync(0xffffffffu, c0 >= qa && c0 + KQW <= qb)) {
+                // Some key of the warp is not seen by all of these queries: hide what it is not
+                // seen by before the exponentials, in a pass of its own so that the common,
                 // unmasked step pays nothing for it.
 #pragma unroll
-                for (int c = 0; c < KQW; ++c)
-                    p[c] = (open && key >= aux.lo[col0 + c] && key < aux.hi[col0 + c]) ? p[c] : -INFINITY;
+                for (int c = 0; c < KQW; ++c) p[c] = (c0 + c >= qa && c0 + c < qb) ? p[c] : -INFINITY;
             }
             {
                 uint32_t pk[KQW / 2];

@@ -106,24 +106,6 @@ __device__ __forceinline__ void row_bounds(const MaskArgs &m, int row, int tq, i
     }
 }
 
-// The same for a query at or after one whose sequence is known: `s` is the sequence of an earlier
-// row (what sequence_of gave for it) and is walked forward to this row's, a step or two instead of
-// a search when consecutive tiles of rows are asked for in turn.
-__device__ __forceinline__ void row_bounds_from(const MaskArgs &m, int &s, int row, int tq, int tk, int &lo, int &hi) {
-    lo = tk;
-    hi = 0;
-    if (row < 0 || row >= tq) return;
-    if (m.kind == 2) {
-        while (s + 1 <= m.seqs && load_index(m.cu_q, m.idx_bytes, s + 1) <= row) ++s;
-        row_bounds_in_sequence(m, s, row, tk, lo, hi);
-    } else {
-        int pos = row + tk - tq;
-        int a = max(0, pos - m.left);
-        int c = min(tk, pos + m.right + 1);
-        if (c > a) { lo = a; hi = c; }
-    }
-}
-
 __device__ __forceinline__ bool key_padded(const MaskArgs &m, int b, int key) {
     if (m.kind != 1) return false;
     int64_t at = (int64_t)b * m.kp_sb + (int64_t)key * m.kp_st;
