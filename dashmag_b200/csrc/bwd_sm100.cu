@@ -575,9 +575,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 // the elementwise work of the step they feed.  With both scores of step t + 1 ready early, a fast
 // warp can finish that step before a slow one has finished step t: the barrier the warps arrive on
 // when dS is written is therefore double as well (one per buffer).
+constexpr int DQ_KS = 3;   // stages of the K ring: a K tile serves S of its step and, a step and a half later, dQ
+
 struct DqBarriers {
     uint64_t res_full;
-    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t k_full[DQ_KS], k_empty[DQ_KS], v_full[2], v_empty[2];
     uint64_t s_full, s_free, dp_full[2], ds_full[2];
     uint64_t acc_ready;
 };
@@ -591,8 +593,8 @@ struct DqTail {
 
 constexpr size_t DQ_TAIL = 1024;
 static_assert(sizeof(DqTail) <= DQ_TAIL, "the tail of the dq kernel's shared memory");
-// 1 KiB slack | Q, dO resident (2 x 32 KiB) | K ring 2 x 32 KiB | V ring 2 x 32 KiB | tail
-constexpr size_t SMEM_DQ = 1024 + 6 * BIG_BYTES + DQ_TAIL;
+// 1 KiB slack | Q, dO resident (2 x 32 KiB) | K ring 3 x 32 KiB | V ring 2 x 32 KiB | tail
+constexpr size_t SMEM_DQ = 1024 + (4 + DQ_KS) * BIG_BYTES + DQ_TAIL;
 constexpr int DQ_THREADS = 32 * (2 + 4 * KCG);
 
 template <typename T>
@@ -603,8 +605,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem, *do_s = q_s + BIG_BYTES;
-    uint8_t *k_s = do_s + BIG_BYTES;          // [2][BIG_BYTES]
-    uint8_t *v_s = k_s + 2 * BIG_BYTES;       // [2][BIG_BYTES]
+    uint8_t *k_s = do_s + BIG_BYTES;          // [DQ_KS][BIG_BYTES]
+    uint8_t *v_s = k_s + DQ_KS * BIG_BYTES;   // [2][BIG_BYTES]
     DqTail &sh = *reinterpret_cast<DqTail *>(v_s + 2 * BIG_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -618,9 +620,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (threadIdx.x == 0) {
         sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
         mbar_init(BAR(sh.bar.res_full), 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < DQ_KS; ++i) {
             mbar_init(BAR(sh.bar.k_full[i]), 1);
             mbar_init(BAR(sh.bar.k_empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(sh.bar.v_full[i]), 1);
             mbar_init(BAR(sh.bar.v_empty[i]), 1);
             mbar_init(BAR(sh.bar.dp_full[i]), 1);
@@ -671,8 +675,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
             for (int t = 0; t < steps; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * BIG;
-                if (!mbar_wait(BAR(sh.bar.k_empty[st]), ph ^ 1)) { failed = true; break; }
-                const uint32_t kf = BAR(sh.bar.k_full[st]), kd = smem_u32(k_s + st * BIG_BYTES);
+                const int ks = t % DQ_KS, kph = (t / DQ_KS) & 1;
+                if (!mbar_wait(BAR(sh.bar.k_empty[ks]), kph ^ 1)) { failed = true; break; }
+                const uint32_t kf = BAR(sh.bar.k_full[ks]), kd = smem_u32(k_s + ks * BIG_BYTES);
                 mbar_expect_tx(kf, BIG_BYTES);
                 tma_load_4d(kd, &tm_k, kf, 0, hk, c0, b);
                 tma_load_4d(kd + BIG_HALF, &tm_k, kf, 64, hk, c0, b);
@@ -694,9 +699,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             auto scores = [&](int t) -> bool {
                 const int st = t & 1, ph = (t >> 1) & 1;
                 if (t > 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_free), (t - 1) & 1))) return false;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[st]), ph))) return false;
+                const int kst = t % DQ_KS, kph = (t / DQ_KS) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[kst]), kph))) return false;
                 tc_fence_after_sync();
-                const uint64_t kk = smem_desc_sw128(smem_u32(k_s + st * BIG_BYTES), 16, 1024);
+                const uint64_t kk = smem_desc_sw128(smem_u32(k_s + kst * BIG_BYTES), 16, 1024);
                 const uint32_t sf = BAR(sh.bar.s_full);
                 if (elect_one()) {
 #pragma unroll
@@ -729,8 +735,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 // dQ += dS K over the step's 128 keys; the K stage is free behind it.
                 if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ds_full[st]), (t >> 1) & 1))) { failed = true; break; }
                 tc_fence_after_sync();
-                const uint64_t km = smem_desc_sw128(smem_u32(k_s + st * BIG_BYTES), BIG_HALF, 1024);
-                const uint32_t ke = BAR(sh.bar.k_empty[st]);
+                const uint64_t km = smem_desc_sw128(smem_u32(k_s + (t % DQ_KS) * BIG_BYTES), BIG_HALF, 1024);
+                const uint32_t ke = BAR(sh.bar.k_empty[t % DQ_KS]);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < BIG / 16; ++ks)
