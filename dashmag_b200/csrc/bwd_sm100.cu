@@ -257,8 +257,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // Key blocks are taken in the order the plan kernel left: the ones most queries see first, so
     // that the longest sweeps start early and the short ones fill the tail.
     const int nkb = (a.tk + BIG - 1) / BIG;
-    const int item = a.order ? a.order[blockIdx.y] : (int)blockIdx.y;
-    const int hk = blockIdx.x, b = item / nkb, kt = item - b * nkb;
+    const int rank = blockIdx.x / a.hkv, hk = blockIdx.x - rank * a.hkv;   // the heads of one key block side by side
+    const int item = a.order ? a.order[rank] : rank;
+    const int b = item / nkb, kt = item - b * nkb;
     const int group = a.hq / a.hkv;
     const int k0 = kt * BIG, k1 = min(k0 + BIG, a.tk);
     auto BAR = [&](uint64_t &x) { return smem_u32(&x); };
@@ -850,8 +851,8 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t 
     } else {
         a.order = nullptr;  // too many to rank in one block (or nothing to rank): index order
     }
-    if (items > 65535) return cudaErrorInvalidConfiguration;
-    dim3 gk(a.hkv, (unsigned)items, 1);
+    if (items * a.hkv > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    dim3 gk((unsigned)(items * a.hkv), 1, 1);
     bwd_dkdv_sm100_kernel<T><<<gk, KTHREADS, SMEM_DKDV, stream>>>(m.k128, m.v128, m.q128, m.do128, a);
     *launches += 1;
     return cudaGetLastError();

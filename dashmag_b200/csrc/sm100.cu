@@ -96,8 +96,7 @@ bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const 
     if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
     if (!q || !k || !v) return false;
     if (!tma_readable(q, p->q_stride) || !tma_readable(k, p->k_stride) || !tma_readable(v, p->v_stride)) return false;
-    if (p->hq > 65535 || p->b > 65535) return false;
-    if (backward && (long long)p->b * ((p->tk + 127) / 128) > 65535) return false;  // the dkdv grid's y extent
+    if (p->hq > 65535 || p->b > 65535) return false;   // grid extents
     if (!device_is_sm100() || !encoder()) return false;
     return true;
 }
