@@ -590,6 +590,7 @@ struct DqTail {
     uint32_t tmem_base;
     unsigned int abort;
     int red_lo[4 * KCG], red_hi[4 * KCG];
+    int tile_bad;   // an elementwise warp gave up: dQ of the tile is not stored
 };
 
 constexpr size_t DQ_TAIL = 1024;
@@ -602,7 +603,7 @@ template <typename T>
 __global__ void __launch_bounds__(DQ_THREADS, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                    const Sm100BwdArgs a) {
+                    const __grid_constant__ CUtensorMap tm_dq, const Sm100BwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem, *do_s = q_s + BIG_BYTES;
@@ -620,6 +621,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
     if (threadIdx.x == 0) {
         sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
+        sh.tile_bad = 0;
         mbar_init(BAR(sh.bar.res_full), 1);
         for (int i = 0; i < DQ_KS; ++i) {
             mbar_init(BAR(sh.bar.k_full[i]), 1);
@@ -639,6 +641,16 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         prefetch_tensormap(&tm_do);
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
+        prefetch_tensormap(&tm_dq);
+        // The resident tiles are on their way before the block knows which keys it sweeps: their
+        // flight covers the rest of the setup.  (A block that turns out to have nothing to do waits
+        // for them at the end: shared memory must not be written behind a block that has left.)
+        const uint32_t full = BAR(sh.bar.res_full);
+        mbar_expect_tx(full, 2 * BIG_BYTES);
+        tma_load_4d(smem_u32(q_s), &tm_q, full, 0, h, m0, b);
+        tma_load_4d(smem_u32(q_s + BIG_HALF), &tm_q, full, 64, h, m0, b);
+        tma_load_4d(smem_u32(do_s), &tm_do, full, 0, h, m0, b);
+        tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -668,12 +680,6 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
     if (warp == 0) {
         if (lane == 0 && steps > 0) {
-            const uint32_t full = BAR(sh.bar.res_full);
-            mbar_expect_tx(full, 2 * BIG_BYTES);
-            tma_load_4d(smem_u32(q_s), &tm_q, full, 0, h, m0, b);
-            tma_load_4d(smem_u32(q_s + BIG_HALF), &tm_q, full, 64, h, m0, b);
-            tma_load_4d(smem_u32(do_s), &tm_do, full, 0, h, m0, b);
-            tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
             for (int t = 0; t < steps; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1, c0 = kmin + t * BIG;
                 const int ks = t % DQ_KS, kph = (t / DQ_KS) & 1;
@@ -811,18 +817,48 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full[st]));
         }
         constexpr int EC = HD / KCG;
-        T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + cg * EC;
         if (steps == 0 || failed) {
+            T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + cg * EC;
             if (row < a.tq && !failed) store_zero_cols<T, 16 / KCG>(dq);
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
+            // Every MMA has completed, so the resident Q is dead: the scaled rows of dQ are staged
+            // over it in the layout of the TMA box and leave as two bulk stores (whole lines instead
+            // of 64 bytes per thread and row; rows past the last query are dropped).
             tc_fence_after_sync();
-            store_acc_cols<T>(t_lane + COL_DQ + cg * EC, dq, a.scale, row < a.tq, EC / 32);
+            uint32_t o[32];
+            tmem_ld32(t_lane + COL_DQ + cg * EC, o);
+            tmem_ld_wait();
+            uint8_t *half_row = q_s + (cg >> 1) * BIG_HALF + r * 128;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                uint4 v;
+                v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * a.scale, __uint_as_float(o[8 * e + 1]) * a.scale);
+                v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * a.scale, __uint_as_float(o[8 * e + 3]) * a.scale);
+                v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * a.scale, __uint_as_float(o[8 * e + 5]) * a.scale);
+                v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * a.scale, __uint_as_float(o[8 * e + 7]) * a.scale);
+                const int chunk = (cg & 1) * 4 + e;   // 16-byte chunk of the half row
+                *reinterpret_cast<uint4 *>(half_row + ((chunk ^ (r & 7)) << 4)) = v;
+            }
             tc_fence_before_sync();
         } else {
             failed = true;
         }
+        if (steps > 0) {
+            // Every elementwise warp gets here (all waits are bounded), whatever became of it: one
+            // that gave up marks the tile, and nothing is stored from a tile that is not whole.
+            if (failed && lane == 0) sh.tile_bad = 1;
+            fence_proxy_async_smem();
+            named_barrier(1, KEW_THREADS);
+            if (sw == 0 && lane == 0 && sh.tile_bad == 0) {
+                tma_store_4d(&tm_dq, smem_u32(q_s), 0, h, m0, b);
+                tma_store_4d(&tm_dq, smem_u32(q_s + BIG_HALF), 64, h, m0, b);
+                tma_store_commit();
+                tma_store_wait_read();
+            }
+        }
     }
 
+    if (threadIdx.x == 0 && steps == 0 && !mbar_wait(BAR(sh.bar.res_full), 0)) failed = true;
     if (failed && !aborted) atomicOr(&g_sm100_bwd_status, 4u);
     tc_fence_before_sync();
     __syncthreads();
@@ -840,7 +876,7 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t 
     e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DQ);
     if (e != cudaSuccess) return e;
     dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
-    bwd_dq_sm100_kernel<T><<<gq, DQ_THREADS, SMEM_DQ, stream>>>(m.q128, m.do128, m.k128, m.v128, a);
+    bwd_dq_sm100_kernel<T><<<gq, DQ_THREADS, SMEM_DQ, stream>>>(m.q128, m.do128, m.k128, m.v128, m.dq128, a);
     *launches += 1;
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);

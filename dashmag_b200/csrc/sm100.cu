@@ -138,7 +138,9 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     *atomic = false;  // both kernels sum in a fixed order whatever `deterministic` says
     Sm100BwdMaps m;
     const void *q = a.q.ptr, *k = a.k.ptr, *v = a.v.ptr, *g = a.dout.ptr;
-    bool ok = encode(&m.q128, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 128) &&
+    const int64_t dq_stride[4] = {(int64_t)p->tq * p->hq * 128, (int64_t)p->hq * 128, 128, 1};   // the gradients are contiguous
+    bool ok = encode(&m.dq128, p->dtype, a.dq, p->b, p->tq, p->hq, dq_stride, 128) &&
+              encode(&m.q128, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 128) &&
               encode(&m.do128, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 128) &&
               encode(&m.k64, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 64) &&
               encode(&m.v64, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 64) &&

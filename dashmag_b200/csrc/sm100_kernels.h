@@ -32,6 +32,7 @@ struct Sm100BwdArgs {
 // and once with boxes of 64 rows (the tiles it streams).
 struct Sm100BwdMaps {
     CUtensorMap q128, do128, k64, v64;   // dq kernel
+    CUtensorMap dq128;                   // dq kernel's output
     CUtensorMap k128, v128, q64, do64;   // dkdv kernel
 };
 
