@@ -18,8 +18,13 @@
 //     and rounds to the queries' dtype.  Chunks past a sequence's length or before its window are
 //     never touched.
 //
+// With 16-bit caches, head dimension 128 and four to sixteen query heads per key-value head the
+// split pass runs on the tensor cores instead (decode_split_mma_kernel below): at that much
+// arithmetic per cache row the FMA pipe, not HBM, bounds the pass above.
+//
 // Inputs the vector path cannot read (head dimension not 64 / 128 / 256, last stride not 1, rows
 // not 16-byte aligned) go through a slower scalar kernel with the same arithmetic.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -273,6 +278,206 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The split pass on the tensor cores (16-bit cache, head dimension 128, groups of up to 16 heads)
+// ---------------------------------------------------------------------------------------------
+// With four or more query heads to a key-value head the scalar pass spends its time on FMA issue,
+// not on HBM: a cache row of 512 bytes feeds 2048 multiply-adds.  Here the query heads of the group
+// are the M dimension of warp-level MMAs (m16n8k16): S = Q K^T with the 16 keys of a tile as two
+// N tiles, then O += P V with P taken straight from the accumulator registers of S as the A
+// operand.  One warp per (chunk, key-value head) as before, with a ring of its own in shared memory:
+// every lane copies 16-byte pieces of the tile's 16 key rows and 16 value rows asynchronously, two
+// tiles ahead, into 256-byte rows whose 16-byte chunks are XOR-swizzled by the row, and ldmatrix
+// reads the fragments from there without bank conflicts (transposed for V).
+constexpr int DM_WARPS = 8;     // warps per block
+constexpr int DM_STAGES = 3;    // tiles of the per-warp ring
+constexpr int DM_KEYS = 16;     // keys per tile
+constexpr int DM_TILE = DM_KEYS * 256;   // bytes of a K (or V) tile: 16 rows of 128 16-bit values
+
+template <typename T> struct MmaType;
+template <> struct MmaType<__nv_bfloat16> {
+    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    static __device__ __forceinline__ float lo(uint32_t u) { return __uint_as_float(u << 16); }
+    static __device__ __forceinline__ float hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+};
+template <> struct MmaType<__half> {
+    static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+    static __device__ __forceinline__ float lo(uint32_t u) { return __low2float(*reinterpret_cast<const __half2 *>(&u)); }
+    static __device__ __forceinline__ float hi(uint32_t u) { return __high2float(*reinterpret_cast<const __half2 *>(&u)); }
+};
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeArgs a) {
+    constexpr int D = 128;
+    extern __shared__ __align__(128) uint8_t dm_ring[];   // [warp][stage][K tile | V tile]
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int group = a.hq / a.hkv;
+    const int b = blockIdx.y;
+    const long long unit = (long long)blockIdx.x * DM_WARPS + wib;
+    const int hk = (int)(unit % a.hkv);
+    const long long split = unit / a.hkv;
+    if (split >= a.splits) return;
+    int first, len;
+    decode_range(a, b, first, len);
+    const long long c0l = (long long)first + split * a.chunk;
+    if (c0l >= len) return;
+    const int c0 = (int)c0l, c1 = min(len, c0 + a.chunk);
+    const int iters = (c1 - c0 + DM_KEYS - 1) / DM_KEYS;
+
+    const int g = lane >> 2, t = lane & 3;   // fragment coordinates: row (head) g and g + 8, column pair t
+    // Q as the A operand of every score MMA: [16 heads x 16 d] per k-step, rows past the group zero.
+    uint32_t qa[D / 16][4];
+    {
+        const T *q0 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g, group - 1)) * a.q_sh;
+        const T *q1 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g + 8, group - 1)) * a.q_sh;
+        const bool live0 = g < group, live1 = g + 8 < group;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qa[ks][0] = live0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 2 * t) : 0u;
+            qa[ks][1] = live1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 2 * t) : 0u;
+            qa[ks][2] = live0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 8 + 2 * t) : 0u;
+            qa[ks][3] = live1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+    const T *kbase = static_cast<const T *>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)hk * a.k.sh;
+    const T *vbase = static_cast<const T *>(a.v.ptr) + (int64_t)b * a.v.sb + (int64_t)hk * a.v.sh;
+    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(dm_ring)) + (uint32_t)wib * DM_STAGES * 2 * DM_TILE;
+
+    // This lane's pieces of a tile: chunk (lane % 16) of rows (lane / 16) + 2 j.
+    const int cp_chunk = lane & 15, cp_row0 = lane >> 4;
+    auto issue = [&](int it) {
+        if (it < iters) {
+            const uint32_t dst = ring + (uint32_t)(it % DM_STAGES) * 2 * DM_TILE;
+#pragma unroll
+            for (int j = 0; j < DM_KEYS / 2; ++j) {
+                const int row = cp_row0 + 2 * j, key = c0 + it * DM_KEYS + row;
+                const bool valid = key < c1;
+                const uint32_t at = (uint32_t)(row * 256 + ((cp_chunk ^ (row & 7)) << 4));
+                cp_async16(dst + at, kbase + (int64_t)(valid ? key : c0) * a.k.st + cp_chunk * 8, valid);
+                cp_async16(dst + DM_TILE + at, vbase + (int64_t)(valid ? key : c0) * a.v.st + cp_chunk * 8, valid);
+            }
+        }
+        cp_async_commit();  // always, so that the group count stays in step with the tiles
+    };
+
+    const float sl = a.scale * 1.4426950408889634f;   // scores are exponentiated in base 2
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // rows g and g + 8; l is this lane's share
+    // ldmatrix rows: lane -> (matrix lane / 8, row lane % 8)
+    const int lm = lane >> 3, lr = lane & 7;
+
+#pragma unroll
+    for (int s = 0; s < DM_STAGES - 1; ++s) issue(s);
+    for (int it = 0; it < iters; ++it) {
+        __syncwarp();   // every lane is done with the stage about to be refilled
+        issue(it + DM_STAGES - 1);
+        cp_async_wait<DM_STAGES - 1>();
+        __syncwarp();   // ... and sees the other lanes' pieces of this tile
+        const uint32_t kt = ring + (uint32_t)(it % DM_STAGES) * 2 * DM_TILE, vt = kt + DM_TILE;
+        const int key0 = c0 + it * DM_KEYS;
+
+        // S[16 heads x 16 keys] as two N tiles of 8 keys.
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int row = nt * 8 + lr;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks += 2) {
+                uint32_t kb[4];   // b0, b1 of k-step ks, then of ks + 1
+                ldmatrix_x4(kt + (uint32_t)(row * 256 + (((2 * ks + lm) ^ (row & 7)) << 4)), kb);
+                MmaType<T>::mma(sc[nt], qa[ks], kb[0], kb[1]);
+                MmaType<T>::mma(sc[nt], qa[ks + 1], kb[2], kb[3]);
+            }
+        }
+        // Online softmax of rows g (values 0, 1 of a tile) and g + 8 (values 2, 3); a tile's columns
+        // are keys key0 + 8 nt + 2 t + {0, 1}.
+        if (key0 + DM_KEYS > c1) {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (key0 + nt * 8 + 2 * t + (j & 1) >= c1) sc[nt][j] = -INFINITY;
+        }
+        // P goes to the tensor cores as the sum of two 16-bit values (what the rounding of the first
+        // loses is the second), so that the products keep the f32 accuracy of the scalar pass.
+        uint32_t pa[4], pl[4];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            float mx = fmaxf(fmaxf(sc[0][2 * rr], sc[0][2 * rr + 1]), fmaxf(sc[1][2 * rr], sc[1][2 * rr + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m[rr], mx);
+            if (__any_sync(0xffffffffu, mn > m[rr])) {
+                // The row's maximum grew (in some row of the warp): bring the sum and the accumulator along.
+                const float corr = mn == -INFINITY ? 1.f : exp2f((m[rr] - mn) * sl);   // exp2(-inf) = 0 for a first maximum
+                l[rr] *= corr;
+#pragma unroll
+                for (int n = 0; n < D / 8; ++n) { o[n][2 * rr] *= corr; o[n][2 * rr + 1] *= corr; }
+                m[rr] = mn;
+            }
+            const float base = m[rr] == -INFINITY ? 0.f : m[rr] * sl;
+            const float p00 = exp2f(fmaf(sc[0][2 * rr], sl, -base)), p01 = exp2f(fmaf(sc[0][2 * rr + 1], sl, -base));
+            const float p10 = exp2f(fmaf(sc[1][2 * rr], sl, -base)), p11 = exp2f(fmaf(sc[1][2 * rr + 1], sl, -base));
+            l[rr] += (p00 + p01) + (p10 + p11);
+            pa[rr] = MmaType<T>::pack(p00, p01);       // a0 / a1: keys 2t, 2t + 1
+            pa[2 + rr] = MmaType<T>::pack(p10, p11);   // a2 / a3: keys 8 + 2t, 8 + 2t + 1
+            pl[rr] = MmaType<T>::pack(p00 - MmaType<T>::lo(pa[rr]), p01 - MmaType<T>::hi(pa[rr]));
+            pl[2 + rr] = MmaType<T>::pack(p10 - MmaType<T>::lo(pa[2 + rr]), p11 - MmaType<T>::hi(pa[2 + rr]));
+        }
+        // O[16 heads x 128 d] += P[16 x 16 keys] V[16 keys x 128 d], two N tiles of 8 d per load.
+#pragma unroll
+        for (int n = 0; n < D / 8; n += 2) {
+            uint32_t vb[4];   // b0, b1 of d-tile n, then of n + 1
+            const int row = (lm & 1) * 8 + lr, chunk = n + (lm >> 1);
+            ldmatrix_x4_trans(vt + (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4)), vb);
+            MmaType<T>::mma(o[n], pa, vb[0], vb[1]);
+            MmaType<T>::mma(o[n], pl, vb[0], vb[1]);
+            MmaType<T>::mma(o[n + 1], pa, vb[2], vb[3]);
+            MmaType<T>::mma(o[n + 1], pl, vb[2], vb[3]);
+        }
+    }
+    cp_async_wait<0>();
+
+    // Each row's sum over the four lanes that share it, then the normalised partial and its log-sum-exp.
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+        l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+        const int hg = g + 8 * rr;
+        if (hg < group) {
+            const int h = hk * group + hg;
+            const float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
+            float *po = a.part_o + (((int64_t)b * a.hq + h) * a.splits + split) * D + 2 * t;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+                *reinterpret_cast<float2 *>(po + n * 8) = make_float2(o[n][2 * rr] * inv, o[n][2 * rr + 1] * inv);
+            if (t == 0) a.part_lse[((int64_t)b * a.hq + h) * a.splits + split] = l[rr] > 0.f ? m[rr] * a.scale + __logf(l[rr]) : -INFINITY;
+        }
+    }
+}
+
 // The same split for inputs the vector loads cannot take: one warp per (chunk, query head), a
 // lane owning the head dimensions `lane + 32 i`, keys in order.
 template <typename T>
@@ -404,9 +609,29 @@ static cudaError_t split_vec(const DecodeArgs &a, cudaStream_t stream) {
 }
 
 template <typename T>
+static cudaError_t split_mma(const DecodeArgs &a, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE;
+    cudaError_t e = cudaFuncSetAttribute(decode_split_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const long long units = (long long)a.splits * a.hkv;
+    dim3 grid((unsigned)((units + DM_WARPS - 1) / DM_WARPS), a.b);
+    decode_split_mma_kernel<T><<<grid, DM_WARPS * 32, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+template <>
+cudaError_t split_mma<float>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }   // never taken: 16-bit caches only
+
+// DASH_ATTN_DECODE_MMA=0 keeps the FMA pass (for comparison runs).
+static bool decode_force_scalar_pass() {
+    static const bool off = [] { const char *e = std::getenv("DASH_ATTN_DECODE_MMA"); return e && std::atoi(e) == 0; }();
+    return off;
+}
+
+template <typename T>
 static cudaError_t decode_t(const DecodeArgs &a, bool vector_ok, cudaStream_t stream, int *launches) {
     cudaError_t e;
-    if (vector_ok && a.d == 64) e = split_vec<T, 64>(a, stream);
+    if (vector_ok && sizeof(T) == 2 && a.d == 128 && a.hq / a.hkv >= 4 && a.hq / a.hkv <= 16 && !decode_force_scalar_pass()) e = split_mma<T>(a, stream);
+    else if (vector_ok && a.d == 64) e = split_vec<T, 64>(a, stream);
     else if (vector_ok && a.d == 128) e = split_vec<T, 128>(a, stream);
     else if (vector_ok && a.d == 256) e = split_vec<T, 256>(a, stream);
     else {
