@@ -219,7 +219,7 @@ struct DkdvBarriers {
     uint64_t res_full;
     uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
     uint64_t aux_full[2];
-    uint64_t s_full, p_full, dp_full, ds_full;
+    uint64_t s_full, p_full[2], dp_full, ds_full[2];   // P^T and dS^T arrive in two halves (even, odd k-steps)
     uint64_t acc_ready;
 };
 
@@ -276,8 +276,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
         mbar_init(BAR(sh.bar.s_full), 1);
         mbar_init(BAR(sh.bar.dp_full), 1);
-        mbar_init(BAR(sh.bar.p_full), 4 * KCG);   // one arrival per elementwise warp
-        mbar_init(BAR(sh.bar.ds_full), 4 * KCG);
+        mbar_init(BAR(sh.bar.p_full[0]), 4 * KCG);   // one arrival per elementwise warp
+        mbar_init(BAR(sh.bar.p_full[1]), 4 * KCG);
+        mbar_init(BAR(sh.bar.ds_full[0]), 4 * KCG);
+        mbar_init(BAR(sh.bar.ds_full[1]), 4 * KCG);
         mbar_init(BAR(sh.bar.acc_ready), 1);
         fence_mbar_init();
         prefetch_tensormap(&tm_k);
@@ -428,36 +430,46 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             if (!failed && !(scores(0) && dscores(0))) failed = true;
             for (int t = 0; t < steps && !failed; ++t) {
                 const int st = t & 1, ph = t & 1;
-                // dV += P^T dO over the step's 128 queries; the dO stage is free behind it.
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full), ph))) { failed = true; break; }
-                tc_fence_after_sync();
+                // dV += P^T dO over the step's 128 queries, the even k-steps (the first half of every
+                // elementwise thread's columns) as soon as they are written, the odd ones behind the
+                // second half; the dO stage is free behind it.
                 {
                     const uint64_t gm = smem_desc_sw128(smem_u32(do_s + st * BIG_BYTES), BIG_HALF, 1024);
                     const uint32_t e = BAR(sh.bar.do_empty[st]);
-                    if (elect_one()) {
 #pragma unroll
-                        for (int ks = 0; ks < QS / 16; ++ks)
-                            umma_f16_ts(tmem + COL_DV, tmem + COL_ST + a_cols(ks), desc_at(gm, ks * 2048), IDESC_ACC,
-                                        (t > 0 || ks > 0) ? 1u : 0u);
-                        umma_commit(e);
+                    for (int half = 0; half < 2; ++half) {
+                        if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[half]), ph))) { failed = true; break; }
+                        tc_fence_after_sync();
+                        if (elect_one()) {
+#pragma unroll
+                            for (int ks = half; ks < QS / 16; ks += 2)
+                                umma_f16_ts(tmem + COL_DV, tmem + COL_ST + a_cols(ks), desc_at(gm, ks * 2048), IDESC_ACC,
+                                            (t > 0 || ks > 0) ? 1u : 0u);
+                            if (half == 1) umma_commit(e);
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
+                    if (failed) break;
                 }
                 if (t + 1 < steps && !scores(t + 1)) { failed = true; break; }
-                // dK += dS^T Q; the Q stage is free behind it.
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ds_full), ph))) { failed = true; break; }
-                tc_fence_after_sync();
+                // dK += dS^T Q likewise; the Q stage is free behind it.
                 {
                     const uint64_t qm = smem_desc_sw128(smem_u32(q_s + st * BIG_BYTES), BIG_HALF, 1024);
                     const uint32_t e = BAR(sh.bar.q_empty[st]);
-                    if (elect_one()) {
 #pragma unroll
-                        for (int ks = 0; ks < QS / 16; ++ks)
-                            umma_f16_ts(tmem + COL_DK, tmem + COL_DPT + a_cols(ks), desc_at(qm, ks * 2048), IDESC_ACC,
-                                        (t > 0 || ks > 0) ? 1u : 0u);
-                        umma_commit(e);
+                    for (int half = 0; half < 2; ++half) {
+                        if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.ds_full[half]), ph))) { failed = true; break; }
+                        tc_fence_after_sync();
+                        if (elect_one()) {
+#pragma unroll
+                            for (int ks = half; ks < QS / 16; ks += 2)
+                                umma_f16_ts(tmem + COL_DK, tmem + COL_DPT + a_cols(ks), desc_at(qm, ks * 2048), IDESC_ACC,
+                                            (t > 0 || ks > 0) ? 1u : 0u);
+                            if (half == 1) umma_commit(e);
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
+                    if (failed) break;
                 }
                 if (t + 1 < steps && !dscores(t + 1)) { failed = true; break; }
             }
@@ -493,25 +505,28 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
                 for (int c = 0; c < KQW; ++c) p[c] = (c0 + c >= qa && c0 + c < qb) ? p[c] : -INFINITY;
             }
-            {
-                uint32_t pk[KQW / 2];
+            // P^T over the first half of the f32 columns this thread has just read, in two halves of
+            // 16 queries (8 columns): the tensor cores start on the first while the second is made.
 #pragma unroll
-                for (int c4 = 0; c4 < KQW / 4; ++c4) {
-                    const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[col0 + c4 * 4]);
-                    p[c4 * 4 + 0] = exp2_mixed<(POLY_OF4 > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2.x));
-                    p[c4 * 4 + 1] = exp2_mixed<(POLY_OF4 > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2.y));
-                    p[c4 * 4 + 2] = exp2_mixed<(POLY_OF4 > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2.z));
-                    p[c4 * 4 + 3] = exp2_mixed<(POLY_OF4 > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2.w));
-                    pk[c4 * 2 + 0] = Pack<T>::two(p[c4 * 4 + 0], p[c4 * 4 + 1]);
-                    pk[c4 * 2 + 1] = Pack<T>::two(p[c4 * 4 + 2], p[c4 * 4 + 3]);
+            for (int half = 0; half < 2; ++half) {
+                uint32_t pk[KQW / 4];
+#pragma unroll
+                for (int c4 = 0; c4 < KQW / 8; ++c4) {
+                    const int c = half * (KQW / 2) + c4 * 4;
+                    const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[col0 + c]);
+                    p[c + 0] = exp2_mixed<(POLY_OF4 > 3)>(fmaf(p[c + 0], a.scale_log2, -l2.x));
+                    p[c + 1] = exp2_mixed<(POLY_OF4 > 1)>(fmaf(p[c + 1], a.scale_log2, -l2.y));
+                    p[c + 2] = exp2_mixed<(POLY_OF4 > 2)>(fmaf(p[c + 2], a.scale_log2, -l2.z));
+                    p[c + 3] = exp2_mixed<(POLY_OF4 > 0)>(fmaf(p[c + 3], a.scale_log2, -l2.w));
+                    pk[c4 * 2 + 0] = Pack<T>::two(p[c + 0], p[c + 1]);
+                    pk[c4 * 2 + 1] = Pack<T>::two(p[c + 2], p[c + 3]);
                 }
-                // P^T over the first half of the f32 columns this thread has just read.
-                tmem_st16(t_lane + COL_ST + col0, pk);
+                tmem_st8(t_lane + COL_ST + col0 + half * (KQW / 4), pk);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[half]));
             }
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(sh.bar.p_full));
 
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full), ph))) { failed = true; break; }
             tc_fence_after_sync();
@@ -519,23 +534,23 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 float dp[KQW];
                 tmem_ld32(t_lane + COL_DPT + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
                 tmem_ld_wait();
-                uint32_t dk[KQW / 2];
 #pragma unroll
-                for (int c4 = 0; c4 < KQW / 4; ++c4) {
-                    const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[col0 + c4 * 4]);
-                    const float d0 = p[c4 * 4 + 0] * (dp[c4 * 4 + 0] - dl.x);
-                    const float d1 = p[c4 * 4 + 1] * (dp[c4 * 4 + 1] - dl.y);
-                    const float d2 = p[c4 * 4 + 2] * (dp[c4 * 4 + 2] - dl.z);
-                    const float d3 = p[c4 * 4 + 3] * (dp[c4 * 4 + 3] - dl.w);
-                    dk[c4 * 2 + 0] = Pack<T>::two(d0, d1);
-                    dk[c4 * 2 + 1] = Pack<T>::two(d2, d3);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t dk[KQW / 4];
+#pragma unroll
+                    for (int c4 = 0; c4 < KQW / 8; ++c4) {
+                        const int c = half * (KQW / 2) + c4 * 4;
+                        const float4 dl = *reinterpret_cast<const float4 *>(&aux.delta[col0 + c]);
+                        dk[c4 * 2 + 0] = Pack<T>::two(p[c + 0] * (dp[c + 0] - dl.x), p[c + 1] * (dp[c + 1] - dl.y));
+                        dk[c4 * 2 + 1] = Pack<T>::two(p[c + 2] * (dp[c + 2] - dl.z), p[c + 3] * (dp[c + 3] - dl.w));
+                    }
+                    tmem_st8(t_lane + COL_DPT + col0 + half * (KQW / 4), dk);   // dS^T likewise, in the same two halves
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full[half]));
                 }
-                tmem_st16(t_lane + COL_DPT + col0, dk);   // dS^T likewise
             }
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full));
         }
         // ---------------- epilogue: each thread its HD / KCG columns of the row ----------------
         constexpr int EC = HD / KCG;
