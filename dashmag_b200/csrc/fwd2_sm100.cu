@@ -54,7 +54,7 @@ constexpr float RESCALE_LOG2 = 8.0f;
 
 struct Barriers {
     uint64_t q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
-    uint64_t s_full[NT], p_full[NT], o_ready[NT];
+    uint64_t s_full[NT], p_full[NT][BN / 32], o_ready[NT];   // P arrives 32 keys (two k-steps of P V) at a time
 };
 
 struct Shared {
@@ -83,6 +83,22 @@ template <> struct Pack<__half> {
         return *reinterpret_cast<uint32_t *>(&v);
     }
 };
+
+// This thread's row of a 128-column f32 accumulator in tensor memory times `factor`.  Rare (the
+// lazy maximum moved) and out of line, so that its registers are not the softmax loop's.
+__device__ __noinline__ void rescale_accumulator(uint32_t taddr, float factor) {
+    tc_fence_after_sync();
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(taddr + c * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+        tmem_st32(taddr + c * 32, o);
+    }
+    tmem_st_wait();
+}
 
 }  // namespace
 
@@ -121,7 +137,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         for (int t = 0; t < NT; ++t) {
             mbar_init(BAR(sh.bar.s_full[t]), 1);
-            mbar_init(BAR(sh.bar.p_full[t]), 4);   // one arrival per softmax warp
+            for (int i = 0; i < BN / 32; ++i) mbar_init(BAR(sh.bar.p_full[t][i]), 4);   // one arrival per softmax warp
             mbar_init(BAR(sh.bar.o_ready[t]), 1);
         }
         fence_mbar_init();
@@ -226,20 +242,25 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             auto issue_pv = [&](int i, int t) -> bool {
                 const int st = i % NS, vph = (i / NS) & 1;
                 if (t == 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full[st]), vph))) return false;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[t]), i & 1))) return false;
-                tc_fence_after_sync();
                 // V rows are keys (the K of this product): 64-column halves KV_HALF apart, 8-key groups 1024 B apart.
                 const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * KV_BYTES), KV_HALF, 1024);
                 const uint32_t orr = BAR(sh.bar.o_ready[t]), ve = BAR(sh.bar.v_empty[st]);
-                if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < BN / 16; ++ks)
-                        umma_f16_ts(tmem + COL_O(t), tmem + COL_S(t) + ks * 8, desc_at(v_desc, ks * 2048), IDESC_O,
-                                    (i > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(orr);
-                    if (t == NT - 1) umma_commit(ve);
+                for (int part = 0; part < BN / 32; ++part) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[t][part]), i & 1))) return false;
+                    tc_fence_after_sync();
+                    if (elect_one()) {
+#pragma unroll
+                        for (int ks = 2 * part; ks < 2 * part + 2; ++ks)
+                            umma_f16_ts(tmem + COL_O(t), tmem + COL_S(t) + ks * 8, desc_at(v_desc, ks * 2048), IDESC_O,
+                                        (i > 0 || ks > 0) ? 1u : 0u);
+                        if (part == BN / 32 - 1) {
+                            umma_commit(orr);
+                            if (t == NT - 1) umma_commit(ve);
+                        }
+                    }
+                    __syncwarp();
                 }
-                __syncwarp();
                 return true;
             };
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_full), 0))) failed = true;
@@ -309,7 +330,14 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float neg = m_ref == -INFINITY ? 0.f : -m_ref * a.scale_log2;
             const float2 neg2 = make_float2(neg, neg);
 
-            // P over the first 64 of the S columns this thread has read, 32 keys (16 columns) at a time.
+            // O holds steps 0..j-1 once P V of step j - 1 has completed (it has: S of this step was
+            // issued behind it); rescale it before any of P V of step j is issued.
+            if (j > 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (j - 1) & 1))) { failed = true; break; }
+                if (__any_sync(0xffffffffu, rescale)) rescale_accumulator(t_lane + COL_O(t), factor);
+            }
+            // P over the first 64 of the S columns this thread has read, 32 keys (16 columns, two
+            // k-steps of P V) at a time: the tensor cores start on a part while the next is made.
             float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
             for (int cc = 0; cc < BN / 32; ++cc) {
@@ -322,31 +350,15 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     pk[e] = Pack<T>::two(p0, p1);
                 }
                 tmem_st16(t_lane + COL_S(t) + cc * 16, pk);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[t][cc]));
             }
             {
                 const float2 tsum = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
                 l += tsum.x + tsum.y;
             }
-            // O holds steps 0..j-1 once P V of step j - 1 has completed; rescale it before P V of step j.
-            if (j > 0) {
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (j - 1) & 1))) { failed = true; break; }
-                if (__any_sync(0xffffffffu, rescale)) {
-                    tc_fence_after_sync();
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(t_lane + COL_O(t) + c * 32, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
-                        tmem_st32(t_lane + COL_O(t) + c * 32, o);
-                    }
-                }
-            }
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[t]));
         }
 
         // ---------------- epilogue ----------------
