@@ -388,9 +388,10 @@ def main():
                     "h2d_bytes_per_step": qd_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
                          "frac": gbs / world / pk["hbm"], "frac_of_nominal_8TBs": gbs / world / 8000.0,
-                         # ncu at batch 8 read 1.0154 x the algorithmic bytes; traffic grows with the cache read
-                         "traffic": dec_bytes * 1.0154, "traffic_unit": "bytes per pass (scaled from the batch-8 capture)",
-                         "kernels": "decode_split_kernel + decode_merge_kernel (pass-level)"},
+                         # ncu at batch 8 read 1.011 x the algorithmic bytes; traffic grows with the cache read
+                         # (profiles/decode_split_mma_batch8.md)
+                         "traffic": dec_bytes * 1.011, "traffic_unit": "bytes per pass (scaled from the batch-8 capture)",
+                         "kernels": "decode_split_mma_kernel + decode_merge_kernel (pass-level)"},
         }
         del kc, vc
 
@@ -412,14 +413,14 @@ def main():
             "roofline": {"bound": "tensor", "achieved": fwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": fwd_tf / tensor_peak, "frac_of_nominal_2250": fwd_tf / 2250.0,
                          "peak_source": pk["source"] + " burst (kernel timed alone)",
-                         # dram read + write of one launch, ncu capture of this workload (profiles/fwd_sm100_config2.md)
-                         "traffic": 303.9e6, "traffic_unit": "bytes per launch",
-                         "kernel": "fwd_sm100_kernel (1 launch per pass)"},
+                         # dram read + write of one launch, ncu capture of this workload (profiles/fwd2_sm100_config2.md)
+                         "traffic": 307.8e6, "traffic_unit": "bytes per launch",
+                         "kernel": "fwd2_sm100_kernel (1 launch per pass)"},
             "roofline_backward": {"bound": "tensor", "achieved": bwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                                   "frac": bwd_tf / tensor_peak, "frac_of_nominal_2250": bwd_tf / 2250.0,
-                                  # delta 0.26 GB + dq 0.45 GB + dkdv 0.99 GB (profiles/bwd_*_config2.md)
-                                  "traffic": 1.70e9, "traffic_unit": "bytes per pass",
-                                  "kernel": "backward pass: generic_delta + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
+                                  # delta 0.27 GB + dq 0.45 GB + dkdv 0.99 GB (profiles/bwd_*_config2.md)
+                                  "traffic": 1.71e9, "traffic_unit": "bytes per pass",
+                                  "kernel": "backward pass: delta128 + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
             "decode": decode,
             "cpu_baseline": None if args.skip_cpu else cpu_baseline(),
         }
