@@ -286,6 +286,15 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         prefetch_tensormap(&tm_v);
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_do);
+        // The resident tiles are on their way before the block knows which queries it sweeps: their
+        // flight covers the rest of the setup.  (A block that turns out to have nothing to do waits
+        // for them at the end: shared memory must not be written behind a block that has left.)
+        const uint32_t rfull = BAR(sh.bar.res_full);
+        mbar_expect_tx(rfull, 2 * BIG_BYTES);
+        tma_load_4d(smem_u32(k_s), &tm_k, rfull, 0, hk, k0, b);
+        tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, rfull, 64, hk, k0, b);
+        tma_load_4d(smem_u32(v_s), &tm_v, rfull, 0, hk, k0, b);
+        tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, rfull, 64, hk, k0, b);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -321,12 +330,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (warp == 0) {
         // ---------------- producer: TMA loads ----------------
         if (lane == 0 && steps > 0) {
-            const uint32_t rfull = BAR(sh.bar.res_full);
-            mbar_expect_tx(rfull, 2 * BIG_BYTES);
-            tma_load_4d(smem_u32(k_s), &tm_k, rfull, 0, hk, k0, b);
-            tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, rfull, 64, hk, k0, b);
-            tma_load_4d(smem_u32(v_s), &tm_v, rfull, 0, hk, k0, b);
-            tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, rfull, 64, hk, k0, b);
             for (int t = 0; t < steps; ++t) {
                 const int st = t & 1, ph = (t >> 1) & 1;
                 const int h = hk * group + t / tiles, q0 = qfirst + (t % tiles) * QS;
@@ -571,6 +574,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     }
 
+    if (threadIdx.x == 0 && steps == 0 && !mbar_wait(BAR(sh.bar.res_full), 0)) failed = true;
     if (failed && !aborted) atomicOr(&g_sm100_bwd_status, 2u);
     tc_fence_before_sync();
     __syncthreads();
