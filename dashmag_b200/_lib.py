@@ -80,6 +80,7 @@ PROTOTYPES = {
     "dash_attn_backward": (ctypes.c_int, [ctypes.POINTER(Params), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                           ctypes.c_size_t, vp]),
     "dash_attn_decode": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
+    "dash_attn_decode_append": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
     "dash_attn_decode_static": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp]),
     "dash_attn_kernels_take": (ctypes.c_int, [ctypes.POINTER(Params), vp, vp, vp, ctypes.c_int]),
     "dash_attn_device_status": (ctypes.c_int, [ctypes.c_int]),

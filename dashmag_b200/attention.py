@@ -246,6 +246,33 @@ def attention_decode(query, key, value, cache_lengths=None, options: AttentionOp
     return out
 
 
+def attention_decode_append(query, new_key, new_value, key, value, cache_lengths, options: AttentionOptions = AttentionOptions()):
+    """The decoding step that first appends: ``new_key`` / ``new_value`` ``[B,Hkv,D]`` are written
+    into the caches ``[B,S,Hkv,D]`` (in place) at position ``cache_lengths[b]`` and the query sees
+    the keys up to and including them - the reference's ``put_along_axis_owned`` on the cache
+    (crates/dash-mag/src/tensor.rs:732-744) followed by ``attention_decode`` with the lengths plus
+    one (crates/dash-ops/src/attention.rs:732-760), in the decoding step's own launches.
+    ``cache_lengths`` are the lengths before the step; a full cache gets no row."""
+    op = "attention_decode_append"
+    if cache_lengths is None:
+        raise ValueError(f"{op}: the lengths are needed: they say where each sequence's new row goes")
+    p, keep = make_decode_params(query, key, value, cache_lengths, options)
+    _check_device(op, query, key, value, new_key, new_value, *keep)
+    want = (key.shape[0], key.shape[2], key.shape[3])
+    for name, t in (("new_key", new_key), ("new_value", new_value)):
+        if tuple(t.shape) != want or t.dtype != key.dtype:
+            raise ValueError(f"{op}: {name} must be {list(want)} of the cache's dtype, got {list(t.shape)} {t.dtype}")
+    new_key, new_value = new_key.contiguous(), new_value.contiguous()
+    lib = _lib.lib()
+    out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
+    ws = _workspace(lib.dash_attn_decode_workspace(ctypes.byref(p)), query.device)
+    rc = lib.dash_attn_decode_append(ctypes.byref(p), _ptr(query), _ptr(new_key), _ptr(new_value), _ptr(key), _ptr(value),
+                                     _ptr(out), _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
+    if rc != _lib.OK:
+        _raise(rc)
+    return out
+
+
 def causal_attention(query, key, value, scale: float):
     """crates/dash-ops/src/attention.rs:764-772."""
     return attention(query, key, value, AttentionMask.none(), AttentionOptions.causal_().with_scale(scale))

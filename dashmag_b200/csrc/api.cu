@@ -151,8 +151,7 @@ int train_path(const dash_attn_params *p, const void *q, const void *k, const vo
 
 // ---- decode ---------------------------------------------------------------------------------
 
-int check_decode(const dash_attn_decode_params *p) {
-    const char *op = "attention_decode";
+int check_decode(const dash_attn_decode_params *p, const char *op = "attention_decode") {
     if (!p) return fail(DASH_ATTN_INVALID, "%s: null parameters", op);
     if (p->dtype != DASH_ATTN_F32 && p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16)
         return fail(DASH_ATTN_INVALID, "%s: the dtype must be f32, bf16 or f16, got code %d", op, p->dtype);
@@ -353,11 +352,12 @@ int dash_attn_backward(const dash_attn_params *p, const void *q, const void *k, 
     return DASH_ATTN_OK;
 }
 
-int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void *k_cache, const void *v_cache,
-                     void *out, void *workspace, size_t workspace_bytes, dash_attn_stream_t stream_) {
-    const char *op = "attention_decode";
+// The decoding step, with (k_new, v_new set) or without the new row written into the cache first.
+static int decode_impl(const char *op, const dash_attn_decode_params *p, const void *q, const void *k_new, const void *v_new,
+                       const void *k_cache, const void *v_cache, void *out, void *workspace, size_t workspace_bytes,
+                       dash_attn_stream_t stream_) {
     g_error.clear();
-    int rc = check_decode(p);
+    int rc = check_decode(p, op);
     if (rc != DASH_ATTN_OK) return rc;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     const size_t eb = elem_bytes(p->dtype);
@@ -381,6 +381,8 @@ int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void
     a.v = view(v_cache, p->v_stride);
     a.lengths = p->lengths;
     a.len_bytes = p->lengths_elem_bytes;
+    a.k_new = k_new;
+    a.v_new = v_new;
     // The window's left side binds only within S + 1 positions (reference.rs:445).
     int64_t none = (int64_t)p->s + 1;
     a.left = (int)((p->has_window && p->window_left >= 0 && p->window_left < none) ? p->window_left : none);
@@ -390,13 +392,32 @@ int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void
                                            align256(sizeof(float) * (size_t)p->b * p->hq * a.splits * p->d));
     a.out = out;
     bool vec = (p->d == 64 || p->d == 128 || p->d == 256) && vector_readable(q, p->q_stride, 3, eb) &&
-               vector_readable(k_cache, p->k_stride, 4, eb) && vector_readable(v_cache, p->v_stride, 4, eb);
+               vector_readable(k_cache, p->k_stride, 4, eb) && vector_readable(v_cache, p->v_stride, 4, eb) &&
+               (!k_new || (reinterpret_cast<uintptr_t>(k_new) % 16 == 0 && reinterpret_cast<uintptr_t>(v_new) % 16 == 0));
     int launches = 0;
     cudaError_t e = dash::launch_decode(p->dtype, a, vec, stream, &launches);
     g_probe[DASH_ATTN_PROBE_KERNEL_LAUNCHES] += launches;
     g_probe[DASH_ATTN_PROBE_GENERIC_RUNS] += 1;
     if (e != cudaSuccess) return cuda_fail(op, e);
     return DASH_ATTN_OK;
+}
+
+int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void *k_cache, const void *v_cache,
+                     void *out, void *workspace, size_t workspace_bytes, dash_attn_stream_t stream_) {
+    return decode_impl("attention_decode", p, q, nullptr, nullptr, k_cache, v_cache, out, workspace, workspace_bytes, stream_);
+}
+
+int dash_attn_decode_append(const dash_attn_decode_params *p, const void *q, const void *k_new, const void *v_new,
+                            void *k_cache, void *v_cache, void *out, void *workspace, size_t workspace_bytes,
+                            dash_attn_stream_t stream_) {
+    const char *op = "attention_decode_append";
+    g_error.clear();
+    int rc = check_decode(p, op);
+    if (rc != DASH_ATTN_OK) return rc;
+    if (!p->lengths) return fail(DASH_ATTN_INVALID, "%s: the lengths are needed: they say where each sequence's new row goes", op);
+    if ((size_t)p->b * p->hkv * p->d != 0 && p->s != 0 && (!k_new || !v_new))
+        return fail(DASH_ATTN_INVALID, "%s: a new row is null", op);
+    return decode_impl(op, p, q, k_new, v_new, k_cache, v_cache, out, workspace, workspace_bytes, stream_);
 }
 
 int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, const void *k_cache,

@@ -161,12 +161,23 @@ struct DecodeArgs {
     float *part_o;              // [B,Hq,splits,D]
     float *part_lse;            // [B,Hq,splits]
     void *out;                  // [B,Hq,D]
+    // The step that also appends: the new key and value rows [B,Hkv,D] (contiguous) go to
+    // position lengths[b] of the cache, where the step already sees them.  Null otherwise.
+    const void *k_new, *v_new;
 };
 
-// The visible keys of sequence b in a decoding step: [first, len).
+// Where the appending step writes sequence b's new row: its length before the step, or -1 when
+// the step does not append or the cache is full.
+__device__ __forceinline__ int decode_append_at(const DecodeArgs &a, int b) {
+    if (!a.k_new || !a.lengths) return -1;
+    const int len = max(load_index(a.lengths, a.len_bytes, b), 0);
+    return len < a.s ? len : -1;
+}
+
+// The visible keys of sequence b in a decoding step: [first, len); the appended row counts.
 __device__ __forceinline__ void decode_range(const DecodeArgs &a, int b, int &first, int &len) {
     len = a.s;
-    if (a.lengths) len = min(max(load_index(a.lengths, a.len_bytes, b), 0), a.s);
+    if (a.lengths) len = min(max(load_index(a.lengths, a.len_bytes, b), 0) + (a.k_new ? 1 : 0), a.s);
     first = max(0, len - 1 - a.left);
     if (a.left > a.s) first = 0;
 }

@@ -170,6 +170,18 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
     }
     const T *kbase = static_cast<const T *>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)hk * a.k.sh + dl * 8;
     const T *vbase = static_cast<const T *>(a.v.ptr) + (int64_t)b * a.v.sb + (int64_t)hk * a.v.sh + dl * 8;
+    // The appending step: the row at `pos` comes from the new rows, and the warp whose chunk holds
+    // it (first pass only) also writes it into the cache.
+    const int pos = decode_append_at(a, b);
+    const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * D + dl * 8;
+    const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * D + dl * 8;
+    if (pos >= c0 && pos < c1 && pass == 0 && sub == 0) {
+#pragma unroll
+        for (int x = 0; x < VPK; ++x) {
+            reinterpret_cast<uint4 *>(const_cast<T *>(kbase) + (int64_t)pos * a.k.st)[x] = reinterpret_cast<const uint4 *>(knew)[x];
+            reinterpret_cast<uint4 *>(const_cast<T *>(vbase) + (int64_t)pos * a.v.st)[x] = reinterpret_cast<const uint4 *>(vnew)[x];
+        }
+    }
 
     uint4 *mine = ring + (size_t)wib * NS * SLOTS * 32 + lane;
     const uint32_t mine_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(mine));
@@ -183,8 +195,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
             for (int u = 0; u < DEC_UNROLL; ++u) {
                 const int key = c0 + it * STEP_KEYS + u * KPW + sub;
                 const bool valid = key < c1;
-                const T *kp = kbase + (int64_t)(valid ? key : c0) * a.k.st;
-                const T *vp = vbase + (int64_t)(valid ? key : c0) * a.v.st;
+                const T *kp = key == pos ? knew : kbase + (int64_t)(valid ? key : c0) * a.k.st;
+                const T *vp = key == pos ? vnew : vbase + (int64_t)(valid ? key : c0) * a.v.st;
 #pragma unroll
                 for (int x = 0; x < VPK; ++x) {
                     cp_async16(dst + (uint32_t)(((2 * u) * VPK + x) * 32 * 16), reinterpret_cast<const char *>(kp) + 16 * x, valid);
@@ -365,6 +377,16 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
 
     // This lane's pieces of a tile: chunk (lane % 16) of rows (lane / 16) + 2 j.
     const int cp_chunk = lane & 15, cp_row0 = lane >> 4;
+    // The appending step: the row at `pos` comes from the new rows, and the warp whose chunk holds
+    // it also writes it into the cache (sixteen lanes the key row, sixteen the value row).
+    const int pos = decode_append_at(a, b);
+    const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * D;
+    const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * D;
+    if (pos >= c0 && pos < c1) {
+        const T *src = (lane < 16 ? knew : vnew) + cp_chunk * 8;
+        T *dst = const_cast<T *>(lane < 16 ? kbase + (int64_t)pos * a.k.st : vbase + (int64_t)pos * a.v.st) + cp_chunk * 8;
+        *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+    }
     auto issue = [&](int it) {
         if (it < iters) {
             const uint32_t dst = ring + (uint32_t)(it % DM_STAGES) * 2 * DM_TILE;
@@ -373,8 +395,8 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
                 const int row = cp_row0 + 2 * j, key = c0 + it * DM_KEYS + row;
                 const bool valid = key < c1;
                 const uint32_t at = (uint32_t)(row * 256 + ((cp_chunk ^ (row & 7)) << 4));
-                cp_async16(dst + at, kbase + (int64_t)(valid ? key : c0) * a.k.st + cp_chunk * 8, valid);
-                cp_async16(dst + DM_TILE + at, vbase + (int64_t)(valid ? key : c0) * a.v.st + cp_chunk * 8, valid);
+                cp_async16(dst + at, (key == pos ? knew : kbase + (int64_t)(valid ? key : c0) * a.k.st) + cp_chunk * 8, valid);
+                cp_async16(dst + DM_TILE + at, (key == pos ? vnew : vbase + (int64_t)(valid ? key : c0) * a.v.st) + cp_chunk * 8, valid);
             }
         }
         cp_async_commit();  // always, so that the group count stays in step with the tiles
@@ -504,13 +526,24 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_scalar_kernel(Dec
                    : 0.f;
         acc[i] = 0.f;
     }
+    // The appending step: the row at `pos` comes from the new rows, and the warp of the group's
+    // first head whose chunk holds it also writes it into the cache.
+    const int pos = decode_append_at(a, b);
+    const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * a.d;
+    const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * a.d;
+    if (pos >= c0 && pos < c1 && h % (a.hq / a.hkv) == 0) {
+        for (int c = lane; c < a.d; c += 32) {
+            const_cast<T *>(static_cast<const T *>(a.k.ptr))[(int64_t)b * a.k.sb + (int64_t)pos * a.k.st + (int64_t)hk * a.k.sh + (int64_t)c * a.k.sd] = knew[c];
+            const_cast<T *>(static_cast<const T *>(a.v.ptr))[(int64_t)b * a.v.sb + (int64_t)pos * a.v.st + (int64_t)hk * a.v.sh + (int64_t)c * a.v.sd] = vnew[c];
+        }
+    }
     float m = -INFINITY, l = 0.f;
     for (int key = c0; key < c1; ++key) {
         float d = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             int c = lane + 32 * i;
-            if (i < ni && c < a.d) d = fmaf(q[i], load_f32<T>(a.k, b, key, hk, c), d);
+            if (i < ni && c < a.d) d = fmaf(q[i], key == pos ? Num<T>::to_f32(knew[c]) : load_f32<T>(a.k, b, key, hk, c), d);
         }
         const float s = warp_sum(d) * a.scale;
         const float mn = fmaxf(m, s);
@@ -519,7 +552,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_scalar_kernel(Dec
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             int c = lane + 32 * i;
-            float v = (i < ni && c < a.d) ? load_f32<T>(a.v, b, key, hk, c) : 0.f;
+            float v = (i < ni && c < a.d) ? (key == pos ? Num<T>::to_f32(vnew[c]) : load_f32<T>(a.v, b, key, hk, c)) : 0.f;
             acc[i] = fmaf(p, v, acc[i] * corr);
         }
         m = mn;

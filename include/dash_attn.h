@@ -141,6 +141,21 @@ int dash_attn_decode(const dash_attn_decode_params *p, const void *q, const void
                      dash_attn_stream_t stream);
 
 /*
+ * The decoding step that first appends: the step's new key and value rows k_new, v_new [B,Hkv,D]
+ * (contiguous, the cache's dtype) are written to position lengths[b] of sequence b's cache, and the
+ * query sees the keys up to and including that row - what the reference's caller gets from
+ * Tensor::put_along_axis_owned on the cache (crates/dash-mag/src/tensor.rs:732-744, the arm's
+ * crates/dash-mag/src/arm/mod.rs:188-199) followed by attention_decode with lengths + 1, in the
+ * launches of the decoding step alone: the warp that owns the chunk holding the position takes
+ * the row from k_new / v_new and stores it into the cache on its way.  p->lengths are the lengths
+ * BEFORE the step and are required (they are not changed: the caller advances them).  A sequence
+ * whose cache is full (lengths[b] >= S) gets no row written and sees all S keys.
+ */
+int dash_attn_decode_append(const dash_attn_decode_params *p, const void *q, const void *k_new,
+                            const void *v_new, void *k_cache, void *v_cache, void *out,
+                            void *workspace, size_t workspace_bytes, dash_attn_stream_t stream);
+
+/*
  * The decoding step for callers that cannot hand over a workspace.  It has no counterpart in the
  * reference, whose launch glue always allocates its partial outputs from Burn's memory pool.
  *

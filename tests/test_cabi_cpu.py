@@ -105,6 +105,21 @@ def test_decode_refusals():
         A.make_decode_params(t(3, 1, 4, 64), t(3, 50, 2, 64), t(3, 50, 2, 64), None, AttentionOptions())
 
 
+def test_decode_append_refusals():
+    """The appending step needs the lengths (they say where the row goes) and both new rows, and
+    otherwise refuses what attention_decode refuses, under its own name."""
+    lib = _lib.lib()
+    p, _ = A.make_decode_params(t(3, 4, 64), t(3, 50, 2, 64), t(3, 50, 2, 64), None, AttentionOptions())
+    rc = lib.dash_attn_decode_append(ctypes.byref(p), None, None, None, None, None, None, None, 0, None)
+    assert rc == _lib.INVALID and _lib.last_error().startswith("attention_decode_append: the lengths are needed")
+    p, _ = A.make_decode_params(t(3, 4, 64), t(3, 50, 2, 64), t(3, 50, 2, 64), torch.zeros(3, dtype=torch.int64), AttentionOptions())
+    rc = lib.dash_attn_decode_append(ctypes.byref(p), None, None, None, None, None, None, None, 0, None)
+    assert rc == _lib.INVALID and _lib.last_error() == "attention_decode_append: a new row is null"
+    p, _ = A.make_decode_params(t(3, 4, 64), t(3, 50, 2, 64), t(3, 50, 2, 64), torch.zeros(2, dtype=torch.int64), AttentionOptions())
+    rc = lib.dash_attn_decode_append(ctypes.byref(p), None, ctypes.c_void_p(256), ctypes.c_void_p(256), None, None, None, None, 0, None)
+    assert rc == _lib.INVALID and _lib.last_error() == "attention_decode_append: the cache lengths are [B] = [3]"
+
+
 def test_workspace_queries_are_pure_functions_of_the_shape():
     lib = _lib.lib()
     q, k = t(1, 300, 8, 128, dtype=torch.bfloat16), t(1, 300, 2, 128, dtype=torch.bfloat16)
