@@ -178,6 +178,10 @@ def decode_cases():
         ("group of 3", [2, 6, 2, 200, 128], [150, 200], 64),
         ("lengths past the cache and negative", [3, 4, 2, 100, 64], [1000, -5, 100], None),
         ("odd head dimension", [2, 4, 2, 77, 40], [77, 30], 10),
+        # the tensor-core split pass (D 128, groups of 4 to 16): both halves of its 16 MMA rows
+        ("group of 16, D128", [2, 32, 2, 300, 128], [300, 123], None),
+        ("group of 12, D128, window", [3, 24, 2, 1100, 128], [1100, 17, 600], 500),
+        ("group of 4, D128, long", [2, 8, 2, 5000, 128], [4999, 2500], None),
     ]
 
 
