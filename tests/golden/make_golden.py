@@ -15,7 +15,7 @@ Layout of each ``.npz`` (torch order ``[B, H, T, D]``, exactly as recorded):
   key_padding      uint8    padding records only (non-zero = key left out)
   meta             str      JSON of the record's metadata (scale, causal, window_left/right, kind)
 
-Run from anywhere:  python tests/golden/make_golden.py [reference_root]
+Run from anywhere:  python tests/golden/make_golden.py <root of the reference checkout>
 """
 import json
 import pathlib
@@ -29,7 +29,9 @@ HERE = pathlib.Path(__file__).resolve().parent
 
 
 def main() -> None:
-    root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <root of the reference checkout>")
+    root = pathlib.Path(sys.argv[1])
     src = root / "crates" / "dash-ops" / "tests" / "fixtures" / "attention"
     out = HERE / "attention"
     out.mkdir(parents=True, exist_ok=True)
