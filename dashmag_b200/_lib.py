@@ -71,6 +71,28 @@ class DecodeParams(ctypes.Structure):
     ]
 
 
+class RopeTables(ctypes.Structure):
+    """``dash_rope_tables``."""
+    _fields_ = [("dtype", i32), ("dim", i32), ("len", i64), ("cos", vp), ("sin", vp)]
+
+
+class RopeParams(ctypes.Structure):
+    """``dash_rope_params``."""
+    _fields_ = [
+        ("tokens", i64),
+        ("d", i32),
+        ("heads_a", i32), ("heads_b", i32),
+        ("stride_a", i64 * 2), ("stride_b", i64 * 2),
+        ("inverse", i32),
+        ("positions", vp),
+        ("positions_elem_bytes", i32),
+        ("cu_seqlens", vp),
+        ("cu_seqlens_len", i32),
+        ("index_elem_bytes", i32),
+        ("start", i64), ("period", i64),
+    ]
+
+
 #: Every symbol ``include/dash_attn.h`` declares, with (restype, argtypes).
 PROTOTYPES = {
     "dash_attn_forward_workspace": (ctypes.c_size_t, [ctypes.POINTER(Params)]),
@@ -81,6 +103,10 @@ PROTOTYPES = {
                                           ctypes.c_size_t, vp]),
     "dash_attn_decode": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
     "dash_attn_decode_append": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
+    "dash_rope_apply": (ctypes.c_int, [ctypes.POINTER(RopeTables), ctypes.POINTER(RopeParams), vp, vp, vp, vp, vp]),
+    "dash_attn_decode_append_rope_workspace": (ctypes.c_size_t, [ctypes.POINTER(DecodeParams)]),
+    "dash_attn_decode_append_rope": (ctypes.c_int, [ctypes.POINTER(DecodeParams), ctypes.POINTER(RopeTables), vp, i32,
+                                                    vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
     "dash_attn_decode_static": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp]),
     "dash_attn_kernels_take": (ctypes.c_int, [ctypes.POINTER(Params), vp, vp, vp, ctypes.c_int]),
     "dash_attn_device_status": (ctypes.c_int, [ctypes.c_int]),

@@ -11,6 +11,7 @@
 #include "../../include/dash_attn.h"
 #include "common.cuh"
 #include "launch.h"
+#include "rope.h"
 #include "sm100.h"
 #include "sm100_kernels.h"
 
@@ -418,6 +419,111 @@ int dash_attn_decode_append(const dash_attn_decode_params *p, const void *q, con
     if ((size_t)p->b * p->hkv * p->d != 0 && p->s != 0 && (!k_new || !v_new))
         return fail(DASH_ATTN_INVALID, "%s: a new row is null", op);
     return decode_impl(op, p, q, k_new, v_new, k_cache, v_cache, out, workspace, workspace_bytes, stream_);
+}
+
+// The checks of Rope::new and Rope::check_features (crates/dash-mag/src/rope.rs:27-32, 76-91).
+static int check_rope(const char *op, const dash_rope_tables *r, int d) {
+    if (!r) return fail(DASH_ATTN_INVALID, "%s: null rotation tables", op);
+    if (r->dtype != DASH_ATTN_F32 && r->dtype != DASH_ATTN_BF16 && r->dtype != DASH_ATTN_F16)
+        return fail(DASH_ATTN_INVALID, "Rope: dtype code %d is not floating", r->dtype);
+    if (r->dim <= 0 || r->dim % 2 != 0) return fail(DASH_ATTN_INVALID, "Rope: %d features; an even number is rotated", r->dim);
+    if (d < r->dim) return fail(DASH_ATTN_INVALID, "Rope: %d features to rotate, of %d", r->dim, d);
+    if (r->len < 0) return fail(DASH_ATTN_INVALID, "Rope: %lld positions", (long long)r->len);
+    if (r->len > 0 && (!r->cos || !r->sin)) return fail(DASH_ATTN_INVALID, "%s: a rotation table is null", op);
+    return DASH_ATTN_OK;
+}
+
+int dash_rope_apply(const dash_rope_tables *r, const dash_rope_params *p, const void *x_a, void *out_a, const void *x_b,
+                    void *out_b, dash_attn_stream_t stream_) {
+    const char *op = "rope_apply";
+    g_error.clear();
+    if (!p) return fail(DASH_ATTN_INVALID, "%s: null parameters", op);
+    int rc = check_rope(op, r, p->d);
+    if (rc != DASH_ATTN_OK) return rc;
+    if (p->tokens < 0 || p->heads_a < 0 || p->heads_b < 0)
+        return fail(DASH_ATTN_INVALID, "%s: no dimension may be negative", op);
+    if (p->positions && p->positions_elem_bytes != 4 && p->positions_elem_bytes != 8)
+        return fail(DASH_ATTN_INVALID, "Rope: positions of %d bytes; i32 or i64", p->positions_elem_bytes);
+    if (!p->positions && p->cu_seqlens && (p->index_elem_bytes != 4 && p->index_elem_bytes != 8))
+        return fail(DASH_ATTN_INVALID, "Rope: offsets of %d bytes; i32 or i64", p->index_elem_bytes);
+    if (!p->positions && p->cu_seqlens && p->cu_seqlens_len < 1)
+        return fail(DASH_ATTN_INVALID, "Rope: the offsets hold at least the first 0");
+    const int64_t work = p->tokens * ((int64_t)p->heads_a + p->heads_b) * p->d;
+    if (!p->positions && !p->cu_seqlens && work != 0) {
+        // apply_range's refusal (:111-117): T positions, all inside the tables.
+        const int64_t t = p->period > 0 ? (p->period < p->tokens ? p->period : p->tokens) : 1;
+        if (p->start < 0 || p->period < 0 || (p->period > 0 && p->tokens % p->period != 0) || p->start + t > r->len)
+            return fail(DASH_ATTN_INVALID, "Rope: positions %lld..%lld of %lld for %lld tokens", (long long)p->start,
+                        (long long)(p->start + t), (long long)r->len, (long long)p->tokens);
+    }
+    if (work == 0) return DASH_ATTN_OK;
+    if ((p->heads_a && (!x_a || !out_a)) || (p->heads_b && (!x_b || !out_b)))
+        return fail(DASH_ATTN_INVALID, "%s: a tensor pointer is null", op);
+    dash::RopeArgs a{};
+    a.a = dash::RopeTensor{x_a, out_a, p->heads_a, p->stride_a[0], p->stride_a[1], p->stride_a[0], p->stride_a[1]};
+    a.b = dash::RopeTensor{x_b, out_b, p->heads_b, p->stride_b[0], p->stride_b[1], p->stride_b[0], p->stride_b[1]};
+    a.tokens = p->tokens; a.d = p->d; a.dim = r->dim;
+    a.cos = r->cos; a.sin = r->sin; a.len = r->len;
+    a.inverse = p->inverse ? 1 : 0;
+    a.positions = p->positions; a.pos_bytes = p->positions_elem_bytes;
+    if (!p->positions && p->cu_seqlens) {
+        a.cu = p->cu_seqlens; a.cu_bytes = p->index_elem_bytes; a.sequences = p->cu_seqlens_len - 1;
+    }
+    a.start = p->start; a.period = p->period;
+    int launches = 0;
+    cudaError_t e = dash::launch_rope(r->dtype, a, reinterpret_cast<cudaStream_t>(stream_), &launches);
+    g_probe[DASH_ATTN_PROBE_KERNEL_LAUNCHES] += launches;
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return DASH_ATTN_OK;
+}
+
+// The rotated query and key sit behind the decoding step's own scratch.
+static size_t rope_scratch_offset(const dash_attn_decode_params *p) { return align256(dash_attn_decode_workspace(p)); }
+
+size_t dash_attn_decode_append_rope_workspace(const dash_attn_decode_params *p) {
+    if (!p || p->b < 0 || p->hq < 0 || p->hkv < 0 || p->d < 0) return 0;
+    const size_t eb = elem_bytes(p->dtype);
+    return rope_scratch_offset(p) + align256((size_t)p->b * p->hq * p->d * eb) + align256((size_t)p->b * p->hkv * p->d * eb);
+}
+
+int dash_attn_decode_append_rope(const dash_attn_decode_params *p, const dash_rope_tables *r, const void *positions,
+                                 int32_t positions_elem_bytes, const void *q, const void *k_new, const void *v_new,
+                                 void *k_cache, void *v_cache, void *out, void *workspace, size_t workspace_bytes,
+                                 dash_attn_stream_t stream_) {
+    const char *op = "attention_decode_append_rope";
+    g_error.clear();
+    int rc = check_decode(p, op);
+    if (rc != DASH_ATTN_OK) return rc;
+    if ((rc = check_rope(op, r, p->d)) != DASH_ATTN_OK) return rc;
+    if (r->dtype != p->dtype) return fail(DASH_ATTN_INVALID, "Rope: dtype code %d under a rotation of code %d", p->dtype, r->dtype);
+    if (!p->lengths) return fail(DASH_ATTN_INVALID, "%s: the lengths are needed: they say where each sequence's new row goes", op);
+    if (positions && positions_elem_bytes != 4 && positions_elem_bytes != 8)
+        return fail(DASH_ATTN_INVALID, "Rope: positions of %d bytes; i32 or i64", positions_elem_bytes);
+    const size_t eb = elem_bytes(p->dtype);
+    if ((size_t)p->b * p->hq * p->d == 0 || p->s == 0)   // nothing to rotate for, or no cache to append to
+        return decode_impl(op, p, q, k_new, v_new, k_cache, v_cache, out, workspace, workspace_bytes, stream_);
+    if (!q || !k_new || !v_new) return fail(DASH_ATTN_INVALID, "%s: a tensor pointer is null", op);
+    if (p->q_stride[2] != 1) return fail(DASH_ATTN_UNSUPPORTED, "%s: the query's features must be contiguous", op);
+    const size_t need = dash_attn_decode_append_rope_workspace(p);
+    if ((rc = check_workspace(op, workspace, workspace_bytes, need)) != DASH_ATTN_OK) return rc;
+    char *q_rot = static_cast<char *>(workspace) + rope_scratch_offset(p);
+    char *k_rot = q_rot + align256((size_t)p->b * p->hq * p->d * eb);
+
+    dash::RopeArgs a{};
+    // The rotated rows are written contiguous, whatever the query's strides.
+    a.a = dash::RopeTensor{q, q_rot, p->hq, p->q_stride[0], p->q_stride[1], (int64_t)p->hq * p->d, (int64_t)p->d};
+    a.b = dash::RopeTensor{k_new, k_rot, p->hkv, (int64_t)p->hkv * p->d, (int64_t)p->d, (int64_t)p->hkv * p->d, (int64_t)p->d};
+    a.tokens = p->b; a.d = p->d; a.dim = r->dim;
+    a.cos = r->cos; a.sin = r->sin; a.len = r->len;
+    a.positions = positions ? positions : p->lengths;
+    a.pos_bytes = positions ? positions_elem_bytes : p->lengths_elem_bytes;
+    int launches = 0;
+    cudaError_t e = dash::launch_rope(p->dtype, a, reinterpret_cast<cudaStream_t>(stream_), &launches);
+    g_probe[DASH_ATTN_PROBE_KERNEL_LAUNCHES] += launches;
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    dash_attn_decode_params rotated = *p;
+    rotated.q_stride[0] = (int64_t)p->hq * p->d; rotated.q_stride[1] = p->d; rotated.q_stride[2] = 1;
+    return decode_impl(op, &rotated, q_rot, k_rot, v_new, k_cache, v_cache, out, workspace, workspace_bytes, stream_);
 }
 
 int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, const void *k_cache,

@@ -156,6 +156,66 @@ int dash_attn_decode_append(const dash_attn_decode_params *p, const void *q, con
                             void *workspace, size_t workspace_bytes, dash_attn_stream_t stream);
 
 /*
+ * Rotary position embedding from tables, transformers' form `x cos + rotate_half(x) sin` over the
+ * first `dim` features of every head (crates/dash-mag/src/rope.rs:11-24: Rope's cosines and sines
+ * [len, dim], each angle rounded once to f32 and once to `dtype`; the caller builds them as
+ * Rope::new does, :43-56).  The reference rotates with whole-tensor operations of the tensors'
+ * dtype (Rope::rotate, :94-107): each product and the sum rounds once to that dtype, and so does
+ * this library, bit for bit.
+ */
+typedef struct dash_rope_tables {
+    int32_t dtype;         /* of cos and sin, and of every tensor rotated with them (:76-83) */
+    int32_t dim;           /* features rotated: even, not 0, at most D (:27-29, :84-91) */
+    int64_t len;           /* positions 0..len the tables hold */
+    const void *cos, *sin; /* [len, dim] contiguous, device memory */
+} dash_rope_tables;
+
+/*
+ * One rotation of up to two tensors [tokens, heads, D] that share their tokens' positions (a
+ * layer's query and key: one launch instead of two).  The position of token n is, first rule that
+ * applies: positions[n]; start + n - cu_seqlens[s] for the packed sequence s that holds n (tokens
+ * of no sequence pass through unchanged); start + n % period - Rope::apply_range on [B,T,H,D] is
+ * tokens = B * T, period = T, start = positions.start (:110-135), Rope::apply_at on [B,H,D] is
+ * tokens = B with positions [B] (:141-165).  A range past the tables is refused as the reference
+ * refuses it; positions read on the device cannot be, and one outside the tables gives NaN in the
+ * rotated features instead of the reference's "garbage" (:137-140) - nothing is read out of bounds.
+ */
+typedef struct dash_rope_params {
+    int64_t tokens;
+    int32_t d;
+    int32_t heads_a, heads_b;           /* heads_b = 0: one tensor */
+    int64_t stride_a[2], stride_b[2];   /* elements: token, head; the features are contiguous */
+    int32_t inverse;                    /* 1: the transpose of the rotation, which the gradient goes through */
+    const void *positions;              /* [tokens] or NULL */
+    int32_t positions_elem_bytes;       /* 4 or 8 */
+    const void *cu_seqlens;             /* [cu_seqlens_len] or NULL */
+    int32_t cu_seqlens_len;
+    int32_t index_elem_bytes;           /* 4 or 8 */
+    int64_t start, period;
+} dash_rope_params;
+
+/* out_a / out_b have x_a / x_b's strides and may be x_a / x_b themselves (in place). */
+int dash_rope_apply(const dash_rope_tables *rope, const dash_rope_params *p, const void *x_a, void *out_a,
+                    const void *x_b, void *out_b, dash_attn_stream_t stream);
+
+/*
+ * The appending decoding step with the rotation in front: q [B,Hq,D] and k_new [B,Hkv,D] are
+ * rotated at each sequence's position lengths[b] (`positions` [B], when not NULL, gives other
+ * positions, e.g. for a cache that slides), then the step is dash_attn_decode_append with the
+ * rotated query and key - the reference's caller does Rope::apply_at on the query, Rope::apply_at
+ * on the key, two put_along_axis_owned and attention_decode, five dispatches, where this is one
+ * call that launches the rotation (both tensors at once, into the workspace) and the decoding
+ * step's own kernels.  The result is bit-identical to dash_rope_apply followed by
+ * dash_attn_decode_append.  q's last stride must be 1.
+ */
+size_t dash_attn_decode_append_rope_workspace(const dash_attn_decode_params *p);
+int dash_attn_decode_append_rope(const dash_attn_decode_params *p, const dash_rope_tables *rope,
+                                 const void *positions, int32_t positions_elem_bytes, const void *q,
+                                 const void *k_new, const void *v_new, void *k_cache, void *v_cache,
+                                 void *out, void *workspace, size_t workspace_bytes,
+                                 dash_attn_stream_t stream);
+
+/*
  * The decoding step for callers that cannot hand over a workspace.  It has no counterpart in the
  * reference, whose launch glue always allocates its partial outputs from Burn's memory pool.
  *

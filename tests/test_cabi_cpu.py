@@ -17,7 +17,7 @@ HEADER = pathlib.Path(__file__).resolve().parent.parent / "include" / "dash_attn
 
 def declared_symbols():
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b(dash_attn_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(dash_(?:attn|rope)_[a-z_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
@@ -32,14 +32,15 @@ def test_library_exports_every_declared_symbol():
 def test_struct_sizes_match_the_header():
     """Compiles a two-line C program's worth of truth: sizeof through the C compiler."""
     import subprocess, tempfile
-    src = f'#include "{HEADER}"\n#include <stdio.h>\nint main(){{printf("%zu %zu", sizeof(dash_attn_params), sizeof(dash_attn_decode_params));}}'
+    src = f'#include "{HEADER}"\n#include <stdio.h>\nint main(){{printf("%zu %zu %zu %zu", sizeof(dash_attn_params), sizeof(dash_attn_decode_params), sizeof(dash_rope_tables), sizeof(dash_rope_params));}}'
     with tempfile.TemporaryDirectory() as tmp:
         c = pathlib.Path(tmp) / "s.c"
         c.write_text(src)
         exe = pathlib.Path(tmp) / "s"
         subprocess.run(["/usr/bin/gcc", str(c), "-o", str(exe)], check=True)
-        a, b = map(int, subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split())
+        a, b, c, d = map(int, subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split())
     assert ctypes.sizeof(_lib.Params) == a and ctypes.sizeof(_lib.DecodeParams) == b
+    assert ctypes.sizeof(_lib.RopeTables) == c and ctypes.sizeof(_lib.RopeParams) == d
 
 
 def forward_refusal(q, k, v, mask=AttentionMask.none(), options=AttentionOptions()):
