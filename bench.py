@@ -9,7 +9,8 @@ D = 128, bf16 inputs, f32 accumulation), through the C ABI.  ``value`` is the wh
 TFLOP/s with inputs resident in HBM, counted as algorithmic work: forward 4 D Hq pairs, backward
 10 D Hq pairs (five products; what a deterministic backward recomputes is not counted).  The same
 line carries the decoding step against a bf16 key-value cache (batch 64, lengths U[1024,32768],
-32 / 8 heads, D = 128) as GB/s of cache read, each pass's roofline fraction against
+32 / 8 heads, D = 128) as GB/s of cache read, the rotation of the step's query and key in front of
+the attention call as GB/s moved, each pass's roofline fraction against
 MEASURED_PEAKS.json, the end-to-end number with host buffers, and the CPU oracle timed on the host
 cores beside it.
 
@@ -39,6 +40,7 @@ ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 TRAIN = dict(seqs=8, lo=512, hi=4096, total=16384, hq=32, hkv=8, d=128)
+ROPE_TRAFFIC = 291.1e6  # dram read + write of one rope_kernel launch on config 2 (profiles/rope_kernel_config2.md)
 DECODE = dict(b=64, lo=1024, hi=32768, s=32768, hq=32, hkv=8, d=128)
 
 
@@ -217,6 +219,7 @@ def main():
     from dashmag_b200 import _lib
     from dashmag_b200 import attention as A
     from dashmag_b200.contract import AttentionMask, AttentionOptions
+    from dashmag_b200.rope import Rope
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the attention path has no CPU fallback")
@@ -339,6 +342,33 @@ def main():
     d2h = sum(t.numel() * 2 for t in host_out.values()) + host_lse.numel() * 4
     del host_out, dev_in
 
+    # ---- rotation of the step's query and key (the prologue in front of the attention call) ----
+    rope = Rope(c["d"], 10000.0, int(max(lens)), torch.bfloat16, device=dev)
+    for _ in range(3):
+        rope.apply_packed(q, cu, other=k)
+    barrier()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rope_reps = max(args.steps, 10)
+    rl0 = _lib.probe("kernel_launches")
+    r0.record()
+    for _ in range(rope_reps):
+        rope.apply_packed(q, cu, other=k)
+    r1.record()
+    barrier()
+    rope_launches = _lib.probe("kernel_launches") - rl0
+    rope_ms = max_over_ranks(r0.elapsed_time(r1) / rope_reps)
+    rope_bytes = 2 * 2 * (q.numel() + k.numel())   # each read once and written once
+    rope_gbs = sum_over_ranks(rope_bytes) / (rope_ms * 1e-3) / 1e9
+    rope_leg = {
+        "metric": "rope_qk_bytes_moved", "value": rope_gbs, "unit": "GB/s", "ms_per_step": rope_ms,
+        "bytes_per_step": rope_bytes, "gpu_launches_per_step": rope_launches / rope_reps,
+        "roofline": {"bound": "hbm", "achieved": rope_gbs / world, "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": rope_gbs / world / pk["hbm"],
+                     # dram read + write of one launch, ncu capture of this workload (profiles/rope_kernel_config2.md)
+                     "traffic": ROPE_TRAFFIC, "traffic_unit": "bytes per launch",
+                     "kernel": "rope_kernel (1 launch rotates Q and K)"},
+    }
+
     # ---- decoding leg ----
     decode = None
     if not args.skip_decode:
@@ -421,6 +451,7 @@ def main():
                                   # delta 0.27 GB + dq 0.45 GB + dkdv 0.99 GB (profiles/bwd_*_config2.md)
                                   "traffic": 1.71e9, "traffic_unit": "bytes per pass",
                                   "kernel": "backward pass: delta128 + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
+            "rope": rope_leg,
             "decode": decode,
             "cpu_baseline": None if args.skip_cpu else cpu_baseline(),
         }
