@@ -1,5 +1,6 @@
 // The training forward on the 5th-generation tensor cores, two query tiles per block: bf16 / f16,
-// head dimension 128.
+// head dimension 128 or 64 (the text below gives the sizes at 128; at 64 the Q / K / V tiles and the O
+// accumulators are half as wide and P V runs 128 x 64 x 16).
 //
 // A block owns TWO tiles of 128 queries that sweep the same keys - two query heads of one
 // key-value group over the same rows (grouped heads, even group size), or two consecutive row
@@ -41,13 +42,18 @@ namespace {
 
 constexpr int BM = 128;                   // queries per tile
 constexpr int BN = 128;                   // keys per step
-constexpr int HD = 128;
 constexpr int NT = 2;                     // query tiles per block
 constexpr int NS = 2;                     // stages of the K and of the V ring
-constexpr int Q_BYTES = BM * HD * 2;      // 32 KiB per tile
-constexpr int Q_HALF = Q_BYTES / 2;       // 128 rows of 128 bytes
-constexpr int KV_BYTES = BN * HD * 2;     // 32 KiB
-constexpr int KV_HALF = KV_BYTES / 2;     // 128 rows of 128 bytes
+constexpr int HALF_BYTES = 128 * 128;     // 128 rows of 64 features (128 bytes): what one TMA box brings
+constexpr int Q_HALF = HALF_BYTES, KV_HALF = HALF_BYTES;
+// A tile of 128 rows is HD / 64 such halves.
+template <int HD> struct Geo {
+    static constexpr int HALVES = HD / 64;
+    static constexpr int Q_BYTES = HALVES * HALF_BYTES;    // 32 KiB per tile at HD = 128
+    static constexpr int KV_BYTES = HALVES * HALF_BYTES;
+    // 1 KiB slack | Q x 2 | K ring | V ring | Shared
+    static constexpr size_t SMEM_BYTES = 1024 + NT * Q_BYTES + 2 * NS * KV_BYTES + 1024;
+};
 constexpr int THREADS = 352;
 constexpr int V_WARP = 10;
 constexpr float RESCALE_LOG2 = 8.0f;
@@ -65,9 +71,6 @@ struct Shared {
     int tile_bad[NT];   // a softmax warp of the tile gave up: its output is not stored
 };
 
-// 1 KiB slack | Q x 2 | K ring | V ring | Shared
-constexpr size_t SMEM_BYTES = 1024 + NT * Q_BYTES + 2 * NS * KV_BYTES + 1024;
-
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
     static constexpr int FMT = 1;
@@ -84,8 +87,9 @@ template <> struct Pack<__half> {
     }
 };
 
-// This thread's row of a 128-column f32 accumulator in tensor memory times `factor`.  Rare (the
+// This thread's row of an HD-column f32 accumulator in tensor memory times `factor`.  Rare (the
 // lazy maximum moved) and out of line, so that its registers are not the softmax loop's.
+template <int HD>
 __device__ __noinline__ void rescale_accumulator(uint32_t taddr, float factor) {
     tc_fence_after_sync();
 #pragma unroll 1
@@ -102,11 +106,12 @@ __device__ __noinline__ void rescale_accumulator(uint32_t taddr, float factor) {
 
 }  // namespace
 
-template <typename T>
+template <typename T, int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const Sm100FwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    constexpr int HALVES = Geo<HD>::HALVES, Q_BYTES = Geo<HD>::Q_BYTES, KV_BYTES = Geo<HD>::KV_BYTES;
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem;                       // [NT][Q_BYTES]
     uint8_t *k_s = q_s + NT * Q_BYTES;         // [NS][KV_BYTES]
@@ -152,8 +157,9 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_expect_tx(qf, NT * Q_BYTES);
         for (int t = 0; t < NT; ++t) {
             const uint32_t dst = smem_u32(q_s + t * Q_BYTES);
-            tma_load_4d(dst, &tm_q, qf, 0, tile_head(t), tile_row0(t), b);
-            tma_load_4d(dst + Q_HALF, &tm_q, qf, 64, tile_head(t), tile_row0(t), b);
+#pragma unroll
+            for (int half = 0; half < HALVES; ++half)
+                tma_load_4d(dst + half * Q_HALF, &tm_q, qf, 64 * half, tile_head(t), tile_row0(t), b);
         }
     }
     if (warp == 1) {
@@ -195,8 +201,8 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!mbar_wait(BAR(sh.bar.k_empty[st]), ph ^ 1)) { failed = true; break; }
                 const uint32_t full = BAR(sh.bar.k_full[st]), dst = smem_u32(k_s + st * KV_BYTES);
                 mbar_expect_tx(full, KV_BYTES);
-                tma_load_4d(dst, &tm_k, full, 0, hk, k0, b);
-                tma_load_4d(dst + KV_HALF, &tm_k, full, 64, hk, k0, b);
+#pragma unroll
+                for (int half = 0; half < HALVES; ++half) tma_load_4d(dst + half * KV_HALF, &tm_k, full, 64 * half, hk, k0, b);
             }
         }
     } else if (warp == V_WARP) {
@@ -207,8 +213,8 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!mbar_wait(BAR(sh.bar.v_empty[st]), ph ^ 1)) { failed = true; break; }
                 const uint32_t full = BAR(sh.bar.v_full[st]), dst = smem_u32(v_s + st * KV_BYTES);
                 mbar_expect_tx(full, KV_BYTES);
-                tma_load_4d(dst, &tm_v, full, 0, hk, k0, b);
-                tma_load_4d(dst + KV_HALF, &tm_v, full, 64, hk, k0, b);
+#pragma unroll
+                for (int half = 0; half < HALVES; ++half) tma_load_4d(dst + half * KV_HALF, &tm_v, full, 64 * half, hk, k0, b);
             }
         }
     } else if (warp == 1) {
@@ -334,7 +340,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // issued behind it); rescale it before any of P V of step j is issued.
             if (j > 0) {
                 if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (j - 1) & 1))) { failed = true; break; }
-                if (__any_sync(0xffffffffu, rescale)) rescale_accumulator(t_lane + COL_O(t), factor);
+                if (__any_sync(0xffffffffu, rescale)) rescale_accumulator<HD>(t_lane + COL_O(t), factor);
             }
             // P over the first 64 of the S columns this thread has read, 32 keys (16 columns, two
             // k-steps of P V) at a time: the tensor cores start on a part while the next is made.
@@ -368,7 +374,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (row < a.tq && !failed) {
                 const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int c = 0; c < 16; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
+                for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
                 a.lse[base] = -INFINITY;
             }
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (steps - 1) & 1))) {
@@ -380,7 +386,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float inv = l > 0.f ? 1.f / l : 0.f;
             uint8_t *stage = q_s + t * Q_BYTES;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
                 tmem_ld32(t_lane + COL_O(t) + c * 32, o);
                 tmem_ld_wait();
@@ -396,7 +402,8 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     *reinterpret_cast<uint4 *>(half_row + ((chunk ^ (r & 7)) << 4)) = v;
                 }
             }
-            if (row < a.tq) a.lse[base] = l > 0.f ? m_ref * a.scale + logf(l) : -INFINITY;
+            // Once per row, so in f64: the product, the logarithm and their sum round once, to f32 at the end.
+            if (row < a.tq) a.lse[base] = l > 0.f ? (float)((double)m_ref * (double)a.scale + log((double)l)) : -INFINITY;
             tc_fence_before_sync();
         } else {
             failed = true;
@@ -409,8 +416,9 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             named_barrier(1 + t, 128);   // the tile's four warps
             if ((warp & 3) == 2 && lane == 0 && sh.tile_bad[t] == 0) {
                 uint8_t *stage = q_s + t * Q_BYTES;
-                tma_store_4d(&tm_o, smem_u32(stage), 0, h, tile_row0(t), b);
-                tma_store_4d(&tm_o, smem_u32(stage + Q_HALF), 64, h, tile_row0(t), b);
+#pragma unroll
+                for (int half = 0; half < HALVES; ++half)
+                    tma_store_4d(&tm_o, smem_u32(stage + half * Q_HALF), 64 * half, h, tile_row0(t), b);
                 tma_store_commit();
                 tma_store_wait_read();
             }
@@ -428,20 +436,26 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
+namespace {
+template <typename T, int HD>
+cudaError_t launch_fwd2_t(dim3 grid, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const CUtensorMap &to,
+                          const Sm100FwdArgs &a, cudaStream_t stream) {
+    constexpr size_t smem = Geo<HD>::SMEM_BYTES;
+    cudaError_t e = cudaFuncSetAttribute(fwd2_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    fwd2_sm100_kernel<T, HD><<<grid, THREADS, smem, stream>>>(tq, tk, tv, to, a);
+    return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_fwd2_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                               const CUtensorMap &to, const Sm100FwdArgs &a, cudaStream_t stream) {
     dim3 grid(a.pair_heads ? a.hq / 2 : a.hq, a.pair_heads ? (a.tq + BM - 1) / BM : (a.tq + NT * BM - 1) / (NT * BM), a.b);
-    cudaError_t e;
-    if (dtype == DASH_ATTN_BF16) {
-        e = cudaFuncSetAttribute(fwd2_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        fwd2_sm100_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, to, a);
-    } else {
-        e = cudaFuncSetAttribute(fwd2_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        fwd2_sm100_kernel<__half><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, to, a);
-    }
-    return cudaGetLastError();
+    if (dtype == DASH_ATTN_BF16)
+        return a.d == 64 ? launch_fwd2_t<__nv_bfloat16, 64>(grid, tq, tk, tv, to, a, stream)
+                         : launch_fwd2_t<__nv_bfloat16, 128>(grid, tq, tk, tv, to, a, stream);
+    return a.d == 64 ? launch_fwd2_t<__half, 64>(grid, tq, tk, tv, to, a, stream)
+                     : launch_fwd2_t<__half, 128>(grid, tq, tk, tv, to, a, stream);
 }
 
 cudaError_t read_sm100_fwd2_status(unsigned int *status, bool clear) {

@@ -364,7 +364,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                 }
             }
-            if (row < a.tq) a.lse[base] = l > 0.f ? m_ref * a.scale + logf(l) : -INFINITY;
+            // Once per row, so in f64: the product, the logarithm and their sum round once, to f32 at the end.
+            if (row < a.tq) a.lse[base] = l > 0.f ? (float)((double)m_ref * (double)a.scale + log((double)l)) : -INFINITY;
             tc_fence_before_sync();
         } else {
             failed = true;

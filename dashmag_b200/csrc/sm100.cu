@@ -63,13 +63,13 @@ bool tma_readable(const void *ptr, const int64_t *stride) {
     return true;
 }
 
-// A [B, T, H, 128] tensor of 16-bit elements as a 4-D map (d, h, t, b) with boxes of 64 x 1 x 128 x 1
-// and the 128-byte swizzle: each load brings 128 rows of 128 bytes of one head.
-bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows = 128) {
+// A [B, T, H, d] tensor of 16-bit elements (d = 128 or 64) as a 4-D map (d, h, t, b) with boxes of
+// 64 x 1 x 128 x 1 and the 128-byte swizzle: each load brings 128 rows of 128 bytes of one head.
+bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows = 128, int d = 128) {
     EncodeTiled fn = encoder();
     if (!fn) return false;
     auto bytes = [](int64_t elems) { return static_cast<cuuint64_t>(elems) * 2; };
-    cuuint64_t dims[4] = {128, (cuuint64_t)h, (cuuint64_t)t, (cuuint64_t)b};
+    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)h, (cuuint64_t)t, (cuuint64_t)b};
     // A dimension of extent 1 never moves: give it any legal stride.
     cuuint64_t strides[3] = {h > 1 ? bytes(stride[2]) : 256, t > 1 ? bytes(stride[1]) : 256, b > 1 ? bytes(stride[0]) : 256};
     for (cuuint64_t s : strides)
@@ -91,7 +91,11 @@ float resolved_scale(const dash_attn_params *p) {
 bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
     if (backward && !tma_readable(q, p->do_stride)) return false;  // dO's strides; its base is checked at launch
     if (p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16) return false;
-    if (p->d != 128) return false;
+    // Head dimension 64: the two-tile forward only (its backward takes the generic kernels), and only
+    // from 128 queries or keys on: below that a block holds a single partial tile, the tensor cores
+    // gain nothing, and the generic kernels' f32 FMA sums keep the log-sum-exp within the one or two
+    // units in the last place that the reference's records allow at those sizes.
+    if (p->d != 128 && !(p->d == 64 && !backward && (p->tq >= 128 || p->tk >= 128))) return false;
     const float scale = resolved_scale(p);
     if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
     if (!q || !k || !v) return false;
@@ -112,23 +116,23 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     const int kv_rows = 128;
     (void)one_tile;
     CUtensorMap tq, tk, tv, to;
-    const int64_t o_stride[4] = {(int64_t)p->tq * p->hq * 128, (int64_t)p->hq * 128, 128, 1};   // the output is contiguous
-    if (!encode(&to, p->dtype, a.out, p->b, p->tq, p->hq, o_stride, 128) ||
-        !encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride, 128) ||
-        !encode(&tk, p->dtype, a.k.ptr, p->b, p->tk, p->hkv, p->k_stride, kv_rows) ||
-        !encode(&tv, p->dtype, a.v.ptr, p->b, p->tk, p->hkv, p->v_stride, kv_rows)) {
+    const int64_t o_stride[4] = {(int64_t)p->tq * p->hq * p->d, (int64_t)p->hq * p->d, p->d, 1};   // the output is contiguous
+    if (!encode(&to, p->dtype, a.out, p->b, p->tq, p->hq, o_stride, 128, p->d) ||
+        !encode(&tq, p->dtype, a.q.ptr, p->b, p->tq, p->hq, p->q_stride, 128, p->d) ||
+        !encode(&tk, p->dtype, a.k.ptr, p->b, p->tk, p->hkv, p->k_stride, kv_rows, p->d) ||
+        !encode(&tv, p->dtype, a.v.ptr, p->b, p->tk, p->hkv, p->v_stride, kv_rows, p->d)) {
         err = "attention: the driver refused a TMA tensor map over the inputs";
         return cudaSuccess;
     }
     Sm100FwdArgs f{};
-    f.b = p->b; f.tq = p->tq; f.tk = p->tk; f.hq = p->hq; f.hkv = p->hkv;
+    f.b = p->b; f.tq = p->tq; f.tk = p->tk; f.hq = p->hq; f.hkv = p->hkv; f.d = p->d;
     f.scale = a.scale;
     f.scale_log2 = a.scale * 1.4426950408889634f;
     f.out = a.out;
     f.lse = a.lse;
     f.mask = a.mask;
     f.pair_heads = ((p->hq / p->hkv) % 2 == 0) ? 1 : 0;
-    cudaError_t e = one_tile ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, to, f, stream);
+    cudaError_t e = (one_tile && p->d == 128) ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, to, f, stream);
     *launches += 1;
     return e;
 }

@@ -10,9 +10,10 @@ namespace dash {
 
 struct Sm100FwdArgs {
     int b, tq, tk, hq, hkv;
+    int d;             // head dimension: 128, or 64 (two-tile kernel only)
     float scale;       // the factor on the scores
     float scale_log2;  // scale * log2(e): the exponentials are base 2
-    void *out;         // [B,Tq,Hq,128] contiguous, the inputs' dtype
+    void *out;         // [B,Tq,Hq,D] contiguous, the inputs' dtype
     float *lse;        // [B,Tq,Hq]
     MaskArgs mask;
     int pair_heads;    // two-tile kernel: the block's tiles are two heads of one group (else two row tiles)

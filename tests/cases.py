@@ -67,8 +67,15 @@ def tiled_cases():
     ]
 
 
-def tensor_core_cases():
-    """Shapes of the tcgen05 path (bf16 / f16, D = 128) with boundaries inside its 128-row tiles."""
+def tensor_core_cases(d: int = 128):
+    """Shapes of the tcgen05 path (bf16 / f16, D = 128; the forward also D = 64) with boundaries
+    inside its 128-row tiles."""
+    if d != 128:
+        return [dataclasses.replace(c, name=c.name.replace("tc ", f"tc D{d} ")) for c in _tensor_core_cases(d)]
+    return _tensor_core_cases(d)
+
+
+def _tensor_core_cases(d: int):
     causal, full = AttentionOptions.causal_(), AttentionOptions()
     lens = [300, 1, 0, 515, 128, 77]
     q_lengths, k_lengths = [150, 3, 260, 0, 131], [170, 299, 260, 9, 120]
@@ -77,14 +84,14 @@ def tensor_core_cases():
     pad[400 + 300:] = True
     none = AttentionMask.none()
     return [
-        seeded("tc causal 1 tile", [1, 4, 2, 128, 128, 128], none, causal, 101),
-        seeded("tc causal ragged", [2, 4, 1, 333, 333, 128], none, causal, 102),
-        seeded("tc none, Tq < Tk", [2, 8, 2, 200, 461, 128], none, full, 103),
-        seeded("tc causal, Tq > Tk", [1, 4, 4, 400, 170, 128], none, causal, 104),
-        seeded("tc causal, window 100", [1, 8, 2, 700, 700, 128], none, causal.with_window(100, 0), 105),
-        seeded("tc window 70 x 45", [1, 4, 2, 300, 520, 128], none, full.with_window(70, 45), 106),
-        seeded("tc packed causal", [1, 8, 2, sum(lens), sum(lens), 128], packed(lens, lens), causal, 107),
-        seeded("tc packed cross, causal, window 140", [1, 4, 2, sum(q_lengths), sum(k_lengths), 128],
+        seeded("tc causal 1 tile", [1, 4, 2, 128, 128, d], none, causal, 101),
+        seeded("tc causal ragged", [2, 4, 1, 333, 333, d], none, causal, 102),
+        seeded("tc none, Tq < Tk", [2, 8, 2, 200, 461, d], none, full, 103),
+        seeded("tc causal, Tq > Tk", [1, 4, 4, 400, 170, d], none, causal, 104),
+        seeded("tc causal, window 100", [1, 8, 2, 700, 700, d], none, causal.with_window(100, 0), 105),
+        seeded("tc window 70 x 45", [1, 4, 2, 300, 520, d], none, full.with_window(70, 45), 106),
+        seeded("tc packed causal", [1, 8, 2, sum(lens), sum(lens), d], packed(lens, lens), causal, 107),
+        seeded("tc packed cross, causal, window 140", [1, 4, 2, sum(q_lengths), sum(k_lengths), d],
                packed(q_lengths, k_lengths), causal.with_window(140, 0), 108),
-        seeded("tc key padding, causal", [2, 4, 2, 400, 400, 128], AttentionMask.key_padding(pad.reshape(2, 400)), causal, 109),
+        seeded("tc key padding, causal", [2, 4, 2, 400, 400, d], AttentionMask.key_padding(pad.reshape(2, 400)), causal, 109),
     ]

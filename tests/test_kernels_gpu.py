@@ -88,6 +88,22 @@ def test_tensor_core_shapes_match_oracle(adapter, case, dtype, deterministic):
     R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
 
 
+TC64_CASES = K.tensor_core_cases(64)
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", TC64_CASES, ids=[c.name for c in TC64_CASES])
+def test_head_dimension_64_runs_the_tensor_core_forward(adapter, case, dtype):
+    """D = 64 from 128 queries or keys on: the forward on the tcgen05 kernel (the probe counts it),
+    the backward on the generic kernels, both within the bounds of the D = 128 shapes."""
+    before = _lib.probe("tensor_core_runs")
+    got = run_case(adapter, case, dtype)
+    assert _lib.probe("tensor_core_runs") == before + 1, "the forward, and only it, ran on the tensor cores"
+    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
+    again = run_case(adapter, case, dtype)
+    assert np.array_equal(got.out, again.out, equal_nan=True) and np.array_equal(got.lse, again.lse)
+
+
 @pytest.mark.parametrize("case", [TILED_CASES[0], TILED_CASES[10], TC_CASES[6]], ids=["none", "packed", "tc packed"])
 def test_same_bits_on_every_run_and_both_ways_of_summing(adapter, case):
     """attention_masks.rs:818-899: deterministic runs repeat to the bit; with atomics o, dk and dv
