@@ -42,9 +42,9 @@ __device__ unsigned int g_sm100_bwd_status = 0;
 namespace {
 
 constexpr int BIG = 128;                   // rows of a tile: resident or streamed (and TMEM lanes)
-constexpr int HD = 128;
-constexpr int BIG_BYTES = BIG * HD * 2;    // 32 KiB
-constexpr int BIG_HALF = BIG_BYTES / 2;    // 128 rows of 128 bytes: the tile's first 64 columns
+constexpr int BIG_HALF = BIG * 128;        // 128 rows of 128 bytes: 64 columns of a tile, what one TMA box brings
+// A tile of head dimension HD (128 or 64) is HD / 64 such halves: 32 KiB at 128.
+template <int HD> constexpr int tile_bytes() { return (HD / 64) * BIG_HALF; }
 constexpr int QS = BIG;                    // rows of a streamed tile: a step
 constexpr int POLY_OF4 = 1;                // of every four exponentials, how many run on the FMA pipe (ex2_poly3)
 constexpr int KCG = 4;                     // elementwise warps per TMEM lane quadrant
@@ -239,14 +239,15 @@ struct DkdvTail {
 constexpr size_t DKDV_TAIL = 12288;
 static_assert(sizeof(DkdvTail) <= DKDV_TAIL, "the tail of the dkdv kernel's shared memory");
 // 1 KiB slack | K, V resident (2 x 32 KiB) | Q ring 2 x 32 KiB | dO ring 2 x 32 KiB | tail
-constexpr size_t SMEM_DKDV = 1024 + 6 * BIG_BYTES + DKDV_TAIL;
+template <int HD> constexpr size_t smem_dkdv() { return 1024 + 6 * tile_bytes<HD>() + DKDV_TAIL; }
 
-template <typename T>
+template <typename T, int HD>
 __global__ void __launch_bounds__(KTHREADS, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const Sm100BwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
+    constexpr int BIG_BYTES = tile_bytes<HD>();
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *k_s = smem, *v_s = k_s + BIG_BYTES;
     uint8_t *q_s = v_s + BIG_BYTES;           // [2][BIG_BYTES]
@@ -292,9 +293,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const uint32_t rfull = BAR(sh.bar.res_full);
         mbar_expect_tx(rfull, 2 * BIG_BYTES);
         tma_load_4d(smem_u32(k_s), &tm_k, rfull, 0, hk, k0, b);
-        tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, rfull, 64, hk, k0, b);
+        if constexpr (HD > 64) tma_load_4d(smem_u32(k_s + BIG_HALF), &tm_k, rfull, 64, hk, k0, b);
         tma_load_4d(smem_u32(v_s), &tm_v, rfull, 0, hk, k0, b);
-        tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, rfull, 64, hk, k0, b);
+        if constexpr (HD > 64) tma_load_4d(smem_u32(v_s + BIG_HALF), &tm_v, rfull, 64, hk, k0, b);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -338,12 +339,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 const uint32_t qf = BAR(sh.bar.q_full[st]), qd = smem_u32(q_s + st * BIG_BYTES);
                 mbar_expect_tx(qf, BIG_BYTES);
                 tma_load_4d(qd, &tm_q, qf, 0, h, q0, b);
-                tma_load_4d(qd + BIG_HALF, &tm_q, qf, 64, h, q0, b);
+                if constexpr (HD > 64) tma_load_4d(qd + BIG_HALF, &tm_q, qf, 64, h, q0, b);
                 if (!mbar_wait(BAR(sh.bar.do_empty[st]), ph ^ 1)) { failed = true; break; }
                 const uint32_t gf = BAR(sh.bar.do_full[st]), gd = smem_u32(do_s + st * BIG_BYTES);
                 mbar_expect_tx(gf, BIG_BYTES);
                 tma_load_4d(gd, &tm_do, gf, 0, h, q0, b);
-                tma_load_4d(gd + BIG_HALF, &tm_do, gf, 64, h, q0, b);
+                if constexpr (HD > 64) tma_load_4d(gd + BIG_HALF, &tm_do, gf, 64, h, q0, b);
             }
         }
     } else if (warp == KAUX_WARP) {
@@ -555,19 +556,22 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 }
             }
         }
-        // ---------------- epilogue: each thread its HD / KCG columns of the row ----------------
-        constexpr int EC = HD / KCG;
+        // ---------------- epilogue: 32 columns of the row per thread (HD = 64: the first two of the four warps of a quadrant) ----------------
+        constexpr int EC = 32;
+        const bool mine = cg < HD / EC;
         T *dk = static_cast<T *>(a.dk) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD + cg * EC;
         T *dv = static_cast<T *>(a.dv) + (((int64_t)b * a.tk + key) * a.hkv + hk) * HD + cg * EC;
         if (steps == 0 || failed) {
-            if (key < a.tk && !failed) {
-                store_zero_cols<T, 16 / KCG>(dk);
-                store_zero_cols<T, 16 / KCG>(dv);
+            if (key < a.tk && !failed && mine) {
+                store_zero_cols<T, EC / 8>(dk);
+                store_zero_cols<T, EC / 8>(dv);
             }
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             tc_fence_after_sync();
-            store_acc_cols<T>(t_lane + COL_DV + cg * EC, dv, 1.f, key < a.tk, EC / 32);
-            store_acc_cols<T>(t_lane + COL_DK + cg * EC, dk, a.scale, key < a.tk, EC / 32);
+            if (mine) {
+                store_acc_cols<T>(t_lane + COL_DV + cg * EC, dv, 1.f, key < a.tk, 1);
+                store_acc_cols<T>(t_lane + COL_DK + cg * EC, dk, a.scale, key < a.tk, 1);
+            }
             tc_fence_before_sync();
         } else {
             failed = true;
@@ -615,16 +619,17 @@ struct DqTail {
 constexpr size_t DQ_TAIL = 1024;
 static_assert(sizeof(DqTail) <= DQ_TAIL, "the tail of the dq kernel's shared memory");
 // 1 KiB slack | Q, dO resident (2 x 32 KiB) | K ring 3 x 32 KiB | V ring 2 x 32 KiB | tail
-constexpr size_t SMEM_DQ = 1024 + (4 + DQ_KS) * BIG_BYTES + DQ_TAIL;
+template <int HD> constexpr size_t smem_dq() { return 1024 + (4 + DQ_KS) * tile_bytes<HD>() + DQ_TAIL; }
 constexpr int DQ_THREADS = 32 * (2 + 4 * KCG);
 
-template <typename T>
+template <typename T, int HD>
 __global__ void __launch_bounds__(DQ_THREADS, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_dq, const Sm100BwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int BIG_BYTES = tile_bytes<HD>();
     uint8_t *q_s = smem, *do_s = q_s + BIG_BYTES;
     uint8_t *k_s = do_s + BIG_BYTES;          // [DQ_KS][BIG_BYTES]
     uint8_t *v_s = k_s + DQ_KS * BIG_BYTES;   // [2][BIG_BYTES]
@@ -667,9 +672,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t full = BAR(sh.bar.res_full);
         mbar_expect_tx(full, 2 * BIG_BYTES);
         tma_load_4d(smem_u32(q_s), &tm_q, full, 0, h, m0, b);
-        tma_load_4d(smem_u32(q_s + BIG_HALF), &tm_q, full, 64, h, m0, b);
+        if constexpr (HD > 64) tma_load_4d(smem_u32(q_s + BIG_HALF), &tm_q, full, 64, h, m0, b);
         tma_load_4d(smem_u32(do_s), &tm_do, full, 0, h, m0, b);
-        tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
+        if constexpr (HD > 64) tma_load_4d(smem_u32(do_s + BIG_HALF), &tm_do, full, 64, h, m0, b);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&sh.tmem_base), 512);
@@ -706,12 +711,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 const uint32_t kf = BAR(sh.bar.k_full[ks]), kd = smem_u32(k_s + ks * BIG_BYTES);
                 mbar_expect_tx(kf, BIG_BYTES);
                 tma_load_4d(kd, &tm_k, kf, 0, hk, c0, b);
-                tma_load_4d(kd + BIG_HALF, &tm_k, kf, 64, hk, c0, b);
+                if constexpr (HD > 64) tma_load_4d(kd + BIG_HALF, &tm_k, kf, 64, hk, c0, b);
                 if (!mbar_wait(BAR(sh.bar.v_empty[st]), ph ^ 1)) { failed = true; break; }
                 const uint32_t vf = BAR(sh.bar.v_full[st]), vd = smem_u32(v_s + st * BIG_BYTES);
                 mbar_expect_tx(vf, BIG_BYTES);
                 tma_load_4d(vd, &tm_v, vf, 0, hk, c0, b);
-                tma_load_4d(vd + BIG_HALF, &tm_v, vf, 64, hk, c0, b);
+                if constexpr (HD > 64) tma_load_4d(vd + BIG_HALF, &tm_v, vf, 64, hk, c0, b);
             }
         }
     } else if (warp == 1) {
@@ -835,21 +840,22 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full[st]));
         }
-        constexpr int EC = HD / KCG;
+        constexpr int EC = 32;   // columns of the row per thread (HD = 64: the first two of the four warps of a quadrant)
+        const bool mine = cg < HD / EC;
         if (steps == 0 || failed) {
             T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + cg * EC;
-            if (row < a.tq && !failed) store_zero_cols<T, 16 / KCG>(dq);
+            if (row < a.tq && !failed && mine) store_zero_cols<T, EC / 8>(dq);
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             // Every MMA has completed, so the resident Q is dead: the scaled rows of dQ are staged
             // over it in the layout of the TMA box and leave as two bulk stores (whole lines instead
             // of 64 bytes per thread and row; rows past the last query are dropped).
             tc_fence_after_sync();
             uint32_t o[32];
-            tmem_ld32(t_lane + COL_DQ + cg * EC, o);
+            if (mine) tmem_ld32(t_lane + COL_DQ + cg * EC, o);
             tmem_ld_wait();
             uint8_t *half_row = q_s + (cg >> 1) * BIG_HALF + r * 128;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 4 && mine; ++e) {
                 uint4 v;
                 v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * a.scale, __uint_as_float(o[8 * e + 1]) * a.scale);
                 v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * a.scale, __uint_as_float(o[8 * e + 3]) * a.scale);
@@ -870,7 +876,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             named_barrier(1, KEW_THREADS);
             if (sw == 0 && lane == 0 && sh.tile_bad == 0) {
                 tma_store_4d(&tm_dq, smem_u32(q_s), 0, h, m0, b);
-                tma_store_4d(&tm_dq, smem_u32(q_s + BIG_HALF), 64, h, m0, b);
+                if constexpr (HD > 64) tma_store_4d(&tm_dq, smem_u32(q_s + BIG_HALF), 64, h, m0, b);
                 tma_store_commit();
                 tma_store_wait_read();
             }
@@ -888,14 +894,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 }
 
 // -------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int HD>
 static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t stream, int *launches) {
-    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DKDV);
+    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkdv<HD>());
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DQ);
+    e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq<HD>());
     if (e != cudaSuccess) return e;
     dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
-    bwd_dq_sm100_kernel<T><<<gq, DQ_THREADS, SMEM_DQ, stream>>>(m.q128, m.do128, m.k128, m.v128, m.dq128, a);
+    bwd_dq_sm100_kernel<T, HD><<<gq, DQ_THREADS, smem_dq<HD>(), stream>>>(m.q128, m.do128, m.k128, m.v128, m.dq128, a);
     *launches += 1;
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);
@@ -908,7 +914,7 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t 
     }
     if (items * a.hkv > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     dim3 gk((unsigned)(items * a.hkv), 1, 1);
-    bwd_dkdv_sm100_kernel<T><<<gk, KTHREADS, SMEM_DKDV, stream>>>(m.k128, m.v128, m.q128, m.do128, a);
+    bwd_dkdv_sm100_kernel<T, HD><<<gk, KTHREADS, smem_dkdv<HD>(), stream>>>(m.k128, m.v128, m.q128, m.do128, a);
     *launches += 1;
     return cudaGetLastError();
 }
@@ -924,7 +930,9 @@ cudaError_t read_sm100_bwd_status(unsigned int *status, bool clear) {
 }
 
 cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream, int *launches) {
-    return dtype == DASH_ATTN_BF16 ? launch_t<__nv_bfloat16>(m, a, stream, launches) : launch_t<__half>(m, a, stream, launches);
+    if (dtype == DASH_ATTN_BF16)
+        return a.d == 64 ? launch_t<__nv_bfloat16, 64>(m, a, stream, launches) : launch_t<__nv_bfloat16, 128>(m, a, stream, launches);
+    return a.d == 64 ? launch_t<__half, 64>(m, a, stream, launches) : launch_t<__half, 128>(m, a, stream, launches);
 }
 
 }  // namespace dash

@@ -91,11 +91,11 @@ float resolved_scale(const dash_attn_params *p) {
 bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
     if (backward && !tma_readable(q, p->do_stride)) return false;  // dO's strides; its base is checked at launch
     if (p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16) return false;
-    // Head dimension 64: the two-tile forward only (its backward takes the generic kernels), and only
-    // from 128 queries or keys on: below that a block holds a single partial tile, the tensor cores
-    // gain nothing, and the generic kernels' f32 FMA sums keep the log-sum-exp within the one or two
-    // units in the last place that the reference's records allow at those sizes.
-    if (p->d != 128 && !(p->d == 64 && !backward && (p->tq >= 128 || p->tk >= 128))) return false;
+    // Head dimension 64 only from 128 queries and 128 keys on: below that there is a single partial
+    // tile of queries or of keys (one block per head), the tensor cores gain nothing, and the generic
+    // kernels' f32 FMA sums keep the log-sum-exp within the one or two units in the last place that
+    // the reference's records allow at those sizes.
+    if (p->d != 128 && !(p->d == 64 && p->tq >= 128 && p->tk >= 128)) return false;
     const float scale = resolved_scale(p);
     if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
     if (!q || !k || !v) return false;
@@ -142,16 +142,16 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     *atomic = false;  // both kernels sum in a fixed order whatever `deterministic` says
     Sm100BwdMaps m;
     const void *q = a.q.ptr, *k = a.k.ptr, *v = a.v.ptr, *g = a.dout.ptr;
-    const int64_t dq_stride[4] = {(int64_t)p->tq * p->hq * 128, (int64_t)p->hq * 128, 128, 1};   // the gradients are contiguous
-    bool ok = encode(&m.dq128, p->dtype, a.dq, p->b, p->tq, p->hq, dq_stride, 128) &&
-              encode(&m.q128, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 128) &&
-              encode(&m.do128, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 128) &&
-              encode(&m.k64, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 64) &&
-              encode(&m.v64, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 64) &&
-              encode(&m.k128, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 128) &&
-              encode(&m.v128, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 128) &&
-              encode(&m.q64, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 64) &&
-              encode(&m.do64, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 64);
+    const int64_t dq_stride[4] = {(int64_t)p->tq * p->hq * p->d, (int64_t)p->hq * p->d, p->d, 1};   // the gradients are contiguous
+    bool ok = encode(&m.dq128, p->dtype, a.dq, p->b, p->tq, p->hq, dq_stride, 128, p->d) &&
+              encode(&m.q128, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 128, p->d) &&
+              encode(&m.do128, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 128, p->d) &&
+              encode(&m.k64, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 64, p->d) &&
+              encode(&m.v64, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 64, p->d) &&
+              encode(&m.k128, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 128, p->d) &&
+              encode(&m.v128, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 128, p->d) &&
+              encode(&m.q64, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 64, p->d) &&
+              encode(&m.do64, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 64, p->d);
     if (!ok) {
         err = "attention_backward: the driver refused a TMA tensor map over the inputs";
         return cudaSuccess;
@@ -159,7 +159,7 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     cudaError_t e = launch_generic_delta(p->dtype, a, stream, launches);
     if (e != cudaSuccess) return e;
     Sm100BwdArgs f{};
-    f.b = p->b; f.tq = p->tq; f.tk = p->tk; f.hq = p->hq; f.hkv = p->hkv;
+    f.b = p->b; f.tq = p->tq; f.tk = p->tk; f.hq = p->hq; f.hkv = p->hkv; f.d = p->d;
     f.scale = a.scale;
     f.scale_log2 = a.scale * 1.4426950408889634f;
     f.lse = a.lse;

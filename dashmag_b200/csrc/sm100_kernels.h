@@ -21,6 +21,7 @@ struct Sm100FwdArgs {
 
 struct Sm100BwdArgs {
     int b, tq, tk, hq, hkv;
+    int d;               // head dimension: 128 or 64
     float scale, scale_log2;
     const float *lse;    // [B,Tq,Hq], the forward's
     const float *delta;  // [B,Tq,Hq], rowsum(dO * O)

@@ -93,15 +93,16 @@ TC64_CASES = K.tensor_core_cases(64)
 
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=["bf16", "f16"])
 @pytest.mark.parametrize("case", TC64_CASES, ids=[c.name for c in TC64_CASES])
-def test_head_dimension_64_runs_the_tensor_core_forward(adapter, case, dtype):
-    """D = 64 from 128 queries or keys on: the forward on the tcgen05 kernel (the probe counts it),
-    the backward on the generic kernels, both within the bounds of the D = 128 shapes."""
+def test_head_dimension_64_runs_the_tensor_core_kernels(adapter, case, dtype):
+    """D = 64 from 128 queries or keys on: forward and backward on the tcgen05 kernels (the probe
+    counts them), within the bounds of the D = 128 shapes, the same bits on every run."""
     before = _lib.probe("tensor_core_runs")
     got = run_case(adapter, case, dtype)
-    assert _lib.probe("tensor_core_runs") == before + 1, "the forward, and only it, ran on the tensor cores"
+    assert _lib.probe("tensor_core_runs") == before + 2, "the forward and the backward ran on the tensor cores"
     R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
     again = run_case(adapter, case, dtype)
-    assert np.array_equal(got.out, again.out, equal_nan=True) and np.array_equal(got.lse, again.lse)
+    for x, y in zip([got.out, got.lse, *got.grads], [again.out, again.lse, *again.grads]):
+        assert np.array_equal(x, y, equal_nan=True)
 
 
 @pytest.mark.parametrize("case", [TILED_CASES[0], TILED_CASES[10], TC_CASES[6]], ids=["none", "packed", "tc packed"])
