@@ -450,7 +450,7 @@ def main():
                                   "frac": bwd_tf / tensor_peak, "frac_of_nominal_2250": bwd_tf / 2250.0,
                                   # delta 0.27 GB + dq 0.45 GB + dkdv 0.99 GB (profiles/bwd_*_config2.md)
                                   "traffic": 1.71e9, "traffic_unit": "bytes per pass",
-                                  "kernel": "backward pass: delta128 + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
+                                  "kernel": "backward pass: delta_rows + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
             "rope": rope_leg,
             "decode": decode,
             "cpu_baseline": None if args.skip_cpu else cpu_baseline(),

@@ -521,13 +521,15 @@ static cudaError_t backward_t(const TrainArgs &a, cudaStream_t stream, int *laun
     return cudaSuccess;
 }
 
-// The same for 16-bit rows of 128 elements that can be read 16 bytes at a time: sixteen lanes a row,
-// two rows a warp, the row's 256 bytes of each tensor in one request.
-template <typename T>
-__global__ void __launch_bounds__(THREADS) delta128_kernel(TrainArgs a) {
-    const int lane = threadIdx.x & 31, sub = lane & 15;
+// The same for 16-bit rows of D = 64, 128 or 256 elements that can be read 16 bytes at a time: D / 8
+// lanes a row (at 128: sixteen lanes a row, two rows a warp), the row's bytes of each tensor in one
+// request.
+template <typename T, int D>
+__global__ void __launch_bounds__(THREADS) delta_rows_kernel(TrainArgs a) {
+    constexpr int LPR = D / 8, RPW = 32 / LPR;   // lanes per row, rows per warp
+    const int lane = threadIdx.x & 31, sub = lane % LPR;
     const int64_t rows = (int64_t)a.b * a.tq * a.hq;
-    const int64_t row = ((int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5)) * 2 + (lane >> 4);
+    const int64_t row = ((int64_t)blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5)) * RPW + lane / LPR;
     float sum = 0.f;
     if (row < rows) {
         const int h = (int)(row % a.hq);
@@ -540,7 +542,7 @@ __global__ void __launch_bounds__(THREADS) delta128_kernel(TrainArgs a) {
         for (int i = 0; i < 8; ++i) sum = fmaf(Num<T>::to_f32(gv[i]), Num<T>::to_f32(ov[i]), sum);
     }
 #pragma unroll
-    for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    for (int off = LPR / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
     if (row < rows && sub == 0) a.delta[row] = sum;
 }
 
@@ -552,9 +554,12 @@ static bool rows_16b(const View4 &v) {
 template <typename T>
 static cudaError_t delta_t(const TrainArgs &a, cudaStream_t stream, int *launches) {
     int64_t rows = (int64_t)a.b * a.tq * a.hq;
-    if (sizeof(T) == 2 && a.d == 128 && rows_16b(a.dout) && rows_16b(a.o)) {
-        const int64_t per_block = 2 * (THREADS / 32);
-        delta128_kernel<T><<<(unsigned)((rows + per_block - 1) / per_block), THREADS, 0, stream>>>(a);
+    if (sizeof(T) == 2 && (a.d == 64 || a.d == 128 || a.d == 256) && rows_16b(a.dout) && rows_16b(a.o)) {
+        const int64_t per_block = (32 / (a.d / 8)) * (THREADS / 32);
+        const unsigned blocks = (unsigned)((rows + per_block - 1) / per_block);
+        if (a.d == 64) delta_rows_kernel<T, 64><<<blocks, THREADS, 0, stream>>>(a);
+        else if (a.d == 128) delta_rows_kernel<T, 128><<<blocks, THREADS, 0, stream>>>(a);
+        else delta_rows_kernel<T, 256><<<blocks, THREADS, 0, stream>>>(a);
         *launches += 1;
         return cudaGetLastError();
     }

@@ -1,4 +1,4 @@
-"""A seeded sweep of shapes over the tensor-core kernels (bf16, D = 128): sizes and masks drawn at
+"""A seeded sweep of shapes over the tensor-core kernels (bf16, D = 128 and D = 64): sizes and masks drawn at
 random so that tile boundaries, sequence boundaries, windows and padding fall in places nobody
 chose, every case against the f64 oracle and run twice for identical bits (the pipelines hand
 tiles between warps through barriers; a lost ordering shows as a run-to-run difference)."""
@@ -20,7 +20,7 @@ def adapter():
     return B200Adapter()
 
 
-def random_cases(count, seed):
+def random_cases(count, seed, d=128):
     rng = np.random.default_rng(seed)
     out = []
     for i in range(count):
@@ -43,17 +43,21 @@ def random_cases(count, seed):
         else:
             b = int(rng.integers(1, 4))
             tq, tk = int(rng.integers(1, 700)), int(rng.integers(1, 700))
+            if d != 128:   # the tensor-core kernels take this head dimension from 128 queries and keys on
+                tq, tk = max(tq, 128), max(tk, 128)
             if rng.random() < 0.5:
                 tk = tq
             mask = AttentionMask.none()
             if masking == 1:
                 mask = AttentionMask.key_padding(oracle.coins(b * tk, float(rng.uniform(0.05, 0.6)), 900 + i).reshape(b, tk))
-        out.append(K.seeded(f"random {i}: b{b} hq{hkv * group} hkv{hkv} tq{tq} tk{tk} kind{kind} mask{masking}",
-                            [b, hkv * group, hkv, tq, tk, 128], mask, options, 1000 + 7 * i))
+        if d != 128 and masking == 2:
+            tq, tk = max(tq, 128), max(tk, 128)   # tokens past the last offset belong to no sequence
+        out.append(K.seeded(f"random {i}: d{d} b{b} hq{hkv * group} hkv{hkv} tq{tq} tk{tk} kind{kind} mask{masking}",
+                            [b, hkv * group, hkv, tq, tk, d], mask, options, 1000 + 7 * i))
     return out
 
 
-CASES = random_cases(40, 20261125)
+CASES = random_cases(40, 20261125) + random_cases(20, 20261126, d=64)
 # o, lse, dq, dk, dv relative to each result's largest value.  The gradients are sums of products of
 # values rounded to bf16 (P, dS: 2^-9 each), so their error grows with the number of terms and the
 # bounds of the fixed shapes (test_kernels_gpu.OWN) are a quarter too tight for shapes drawn at
