@@ -93,6 +93,22 @@ class RopeParams(ctypes.Structure):
     ]
 
 
+class SampleParams(ctypes.Structure):
+    """``dash_sample_params``."""
+    _fields_ = [
+        ("dtype", i32),
+        ("b", i32), ("v", i32),
+        ("row_stride", i64),
+        ("temperature", f32),
+        ("top_k", i64),
+        ("top_p", f32),
+        ("seed", ctypes.c_uint64), ("offset", ctypes.c_uint64),
+        ("masked", ctypes.POINTER(ctypes.c_uint32)),
+        ("masked_len", i32),
+        ("token_elem_bytes", i32),
+    ]
+
+
 #: Every symbol ``include/dash_attn.h`` declares, with (restype, argtypes).
 PROTOTYPES = {
     "dash_attn_forward_workspace": (ctypes.c_size_t, [ctypes.POINTER(Params)]),
@@ -107,6 +123,8 @@ PROTOTYPES = {
     "dash_attn_decode_append_rope_workspace": (ctypes.c_size_t, [ctypes.POINTER(DecodeParams)]),
     "dash_attn_decode_append_rope": (ctypes.c_int, [ctypes.POINTER(DecodeParams), ctypes.POINTER(RopeTables), vp, i32,
                                                     vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
+    "dash_sample_workspace": (ctypes.c_size_t, [ctypes.POINTER(SampleParams)]),
+    "dash_sample": (ctypes.c_int, [ctypes.POINTER(SampleParams), vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]),
     "dash_attn_decode_static": (ctypes.c_int, [ctypes.POINTER(DecodeParams), vp, vp, vp, vp, vp]),
     "dash_attn_kernels_take": (ctypes.c_int, [ctypes.POINTER(Params), vp, vp, vp, ctypes.c_int]),
     "dash_attn_device_status": (ctypes.c_int, [ctypes.c_int]),

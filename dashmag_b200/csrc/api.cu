@@ -6,12 +6,15 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <string>
+#include <vector>
 
 #include "../../include/dash_attn.h"
 #include "common.cuh"
 #include "launch.h"
 #include "rope.h"
+#include "sample.h"
 #include "sm100.h"
 #include "sm100_kernels.h"
 
@@ -524,6 +527,79 @@ int dash_attn_decode_append_rope(const dash_attn_decode_params *p, const dash_ro
     dash_attn_decode_params rotated = *p;
     rotated.q_stride[0] = (int64_t)p->hq * p->d; rotated.q_stride[1] = p->d; rotated.q_stride[2] = 1;
     return decode_impl(op, &rotated, q_rot, k_rot, v_new, k_cache, v_cache, out, workspace, workspace_bytes, stream_);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Sampling (crates/dash-ops/src/sample.rs:300-342: the checks, same words)
+// ------------------------------------------------------------------------------------------------
+static int check_sample(const dash_sample_params *p, std::vector<uint32_t> *masked) {
+    const char *op = "sample";
+    if (!p) return fail(DASH_ATTN_INVALID, "%s: null parameters", op);
+    if (p->dtype != DASH_ATTN_F32 && p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16)
+        return fail(DASH_ATTN_INVALID, "%s: logits must be f32, bf16 or f16, got code %d", op, p->dtype);
+    if (p->b < 0 || p->v < 0) return fail(DASH_ATTN_INVALID, "%s: logits must be [B, V], got [%d, %d]", op, p->b, p->v);
+    if (p->v == 0) return fail(DASH_ATTN_INVALID, "%s: the vocabulary is empty", op);
+    if (!(std::isfinite(p->temperature) && p->temperature >= 0.f))
+        return fail(DASH_ATTN_INVALID, "%s: the temperature must be finite and >= 0, got %g", op, (double)p->temperature);
+    if (!(p->top_p >= 0.f && p->top_p <= 1.f))
+        return fail(DASH_ATTN_INVALID, "%s: top_p must be within 0..=1, got %g", op, (double)p->top_p);
+    if (p->top_k < 0) return fail(DASH_ATTN_INVALID, "%s: top_k must not be negative", op);
+    if (p->masked_len < 0 || (p->masked_len > 0 && !p->masked)) return fail(DASH_ATTN_INVALID, "%s: the masked ids are null", op);
+    if (p->token_elem_bytes != 4 && p->token_elem_bytes != 8)
+        return fail(DASH_ATTN_INVALID, "%s: tokens of %d bytes; i32 or i64", op, p->token_elem_bytes);
+    masked->assign(p->masked, p->masked + p->masked_len);
+    std::sort(masked->begin(), masked->end());
+    masked->erase(std::unique(masked->begin(), masked->end()), masked->end());
+    if (!masked->empty()) {
+        if (masked->back() >= (uint32_t)p->v)
+            return fail(DASH_ATTN_INVALID, "%s: masked token id %u is outside the vocabulary of %d", op, masked->back(), p->v);
+        if (masked->size() >= (size_t)p->v) return fail(DASH_ATTN_INVALID, "%s: every token of the vocabulary is masked", op);
+    }
+    return DASH_ATTN_OK;
+}
+
+size_t dash_sample_workspace(const dash_sample_params *p) {
+    if (!p || p->masked_len <= 0 || p->v <= 0) return 0;
+    return align256(sizeof(uint32_t) * (((size_t)p->v + 31) / 32));
+}
+
+int dash_sample(const dash_sample_params *p, const void *logits, void *tokens, float *logprob, float *tempered_logprob,
+                float *sampling_logprob, void *workspace, size_t workspace_bytes, dash_attn_stream_t stream_) {
+    const char *op = "sample";
+    g_error.clear();
+    std::vector<uint32_t> masked;
+    int rc = check_sample(p, &masked);
+    if (rc != DASH_ATTN_OK) return rc;
+    if (p->b == 0) return DASH_ATTN_OK;
+    if (!logits || !tokens || !logprob || !tempered_logprob || !sampling_logprob)
+        return fail(DASH_ATTN_INVALID, "%s: a tensor pointer is null", op);
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if ((rc = check_workspace(op, workspace, workspace_bytes, dash_sample_workspace(p))) != DASH_ATTN_OK) return rc;
+    dash::SampleArgs a{};
+    a.logits = logits; a.b = p->b; a.v = p->v; a.stride = p->row_stride;
+    a.greedy = p->temperature == 0.f;
+    a.tau = a.greedy ? 1.f : std::min(1.0f / p->temperature, 3.4028234663852886e38f);   // Cuts::inverse_temperature (:89-91)
+    const size_t unmasked = (size_t)p->v - masked.size();
+    a.top_k = (p->top_k > 0 && (uint64_t)p->top_k < unmasked) ? (int)p->top_k : 0;        // Cuts::top_k_cut (:93-95)
+    a.has_p = p->top_p < 1.f;                                                              // Cuts::top_p_cut (:97-99)
+    a.p = p->top_p;
+    a.key0 = (uint32_t)p->seed; a.key1 = (uint32_t)(p->seed >> 32);
+    a.off_lo = (uint32_t)p->offset; a.off_hi = (uint32_t)(p->offset >> 32);
+    if (!masked.empty()) {
+        std::vector<uint32_t> bits(((size_t)p->v + 31) / 32, 0u);
+        for (uint32_t id : masked) bits[id >> 5] |= 1u << (id & 31);
+        // From pageable memory: the copy is staged before the call returns, so `bits` may go.
+        cudaError_t e = cudaMemcpyAsync(workspace, bits.data(), bits.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+        a.masked_bits = static_cast<const uint32_t *>(workspace);
+    }
+    a.tokens = tokens; a.token_bytes = p->token_elem_bytes;
+    a.logprob = logprob; a.tempered = tempered_logprob; a.sampling = sampling_logprob;
+    int launches = 0;
+    cudaError_t e = dash::launch_sample(p->dtype, a, stream, &launches);
+    g_probe[DASH_ATTN_PROBE_KERNEL_LAUNCHES] += launches;
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return DASH_ATTN_OK;
 }
 
 int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, const void *k_cache,

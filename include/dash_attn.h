@@ -216,6 +216,38 @@ int dash_attn_decode_append_rope(const dash_attn_decode_params *p, const dash_ro
                                  dash_attn_stream_t stream);
 
 /*
+ * Sampling the next token on the device, the step on the far side of the decoding loop: from the
+ * logits [B, V] of one position per sequence, one token id per row with its log-probability under
+ * the model's distribution, the model's at the temperature, and the one it was drawn from - the
+ * definition of crates/dash-contract/src/sample.rs:1-96 (temperature, top-k, then top-p over what
+ * top-k keeps, ties kept, masked ids taking part in nothing; greedy at temperature 0; Gumbel-max
+ * over Philox4x32-10 words with the key (seed) and the counter (i / 4, row, offset)).  Mirrors
+ * dash-ops' `sample` (crates/dash-ops/src/sample.rs) with SampleOptions
+ * (crates/dash-contract/src/sample.rs:98-150) flattened in, and refuses what it refuses
+ * (crates/dash-ops/src/sample.rs:300-342), in its words.  The same seed, offset and logits give
+ * the same bits on every run.  Not differentiable.
+ */
+typedef struct dash_sample_params {
+    int32_t dtype;            /* of the logits: DASH_ATTN_F32 / BF16 / F16 */
+    int32_t b, v;             /* rows, vocabulary */
+    int64_t row_stride;       /* elements between rows; the vocabulary is contiguous */
+    float temperature;        /* >= 0, finite; 0 = greedy */
+    int64_t top_k;            /* 0 keeps all */
+    float top_p;              /* 0..=1; 1 keeps all */
+    uint64_t seed, offset;    /* the generator's key and counter: advance the offset every step */
+    const uint32_t *masked;   /* HOST memory (they are options, a Vec<u32> in the reference): ids in any order, each < V */
+    int32_t masked_len;
+    int32_t token_elem_bytes; /* 4 (i32) or 8 (i64): the tokens' integer type */
+} dash_sample_params;
+
+/* Bytes of device scratch (the masked ids as a bit per token; 0 without any). */
+size_t dash_sample_workspace(const dash_sample_params *p);
+/* tokens [B] of token_elem_bytes; logprob, tempered_logprob, sampling_logprob [B] f32; all device memory. */
+int dash_sample(const dash_sample_params *p, const void *logits, void *tokens, float *logprob,
+                float *tempered_logprob, float *sampling_logprob, void *workspace,
+                size_t workspace_bytes, dash_attn_stream_t stream);
+
+/*
  * The decoding step for callers that cannot hand over a workspace.  It has no counterpart in the
  * reference, whose launch glue always allocates its partial outputs from Burn's memory pool.
  *

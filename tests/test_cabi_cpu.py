@@ -17,7 +17,7 @@ HEADER = pathlib.Path(__file__).resolve().parent.parent / "include" / "dash_attn
 
 def declared_symbols():
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"\b(dash_(?:attn|rope)_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(dash_(?:attn|rope|sample)[a-z_]*)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
