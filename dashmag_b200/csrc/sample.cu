@@ -4,19 +4,23 @@
 // temperature, top-k, top-p and masked ids; greedy at temperature 0; Gumbel-max with
 // Philox4x32-10 words, counter (i / 4, row, offset), word i % 4 (crates/dash-ops/src/sample/philox.rs).
 //
-// One block per row, the row read from L2 in each pass (a row of 128 Ki bf16 logits is 256 KiB):
+// One thread-block cluster per row (1 to 8 blocks of 1024 threads, as many as fill the GPU at the
+// call's batch; their partial results meet through distributed shared memory), the row read from
+// L2 in each pass (a row of 128 Ki bf16 logits is 256 KiB):
 //   1. the row's maximum over the unmasked tokens, 2. sum exp(z - m) -> the log-sum-exp,
-//   3. the cuts as ONE threshold on the logits' order-preserving integer keys, found by bisection
-//      from the top bit down: top-k's is the largest key T with |{key >= T}| >= k, top-p's the
-//      largest T (at or above top-k's) whose tempered mass reaches p of the mass top-k keeps - every
-//      token tied with the last one is kept by construction, as the definition wants.  16 passes
-//      for 16-bit logits (their keys are their own 16 bits), 32 for f32;
+//   3. the cuts as ONE threshold on the logits' order-preserving integer keys, found by a radix
+//      search from the top byte down: top-k's is the largest key T with |{key >= T}| >= k, top-p's
+//      the largest T (at or above top-k's) whose tempered mass reaches p of the mass top-k keeps -
+//      every token tied with the last one is kept by construction, as the definition wants.  Two
+//      passes for 16-bit logits (their keys are their own 16 bits), four for f32, and all but the
+//      first look only at the tokens that share the bytes found so far;
 //   4. argmax over the kept tokens of s_i + g_i, ties to the lowest id, four tokens per Philox call;
 //   5. the three log-probabilities, taken from one another where the definition says they are one
 //      number (tau = 1; nothing cut).
 // Every sum is formed in a fixed order - each thread its strided elements in sequence, then a
-// tree over the lanes and the warps - so the same call gives the same bits on every run, and the
+// tree over the lanes and the warps, then the cluster's blocks in rank order - so the same call gives the same bits on every run, and the
 // rounding grows with log V as in the reference's trees of pairs (reference.rs:198-214).
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -26,7 +30,9 @@
 namespace dash {
 namespace {
 
-constexpr int ST = 1024;   // threads per row
+namespace cg = cooperative_groups;
+
+constexpr int ST = 1024;   // threads per block; a row has 1 to 8 blocks (a cluster)
 
 // A row's logits as f32 and as integers in the logits' order.
 template <typename T> struct Key;
@@ -71,6 +77,22 @@ __device__ __forceinline__ X block_reduce(X x, Op op, X *scratch) {
     return x;
 }
 
+// The row's reduction: the block's, then the cluster's blocks in rank order through distributed
+// shared memory (`slot` is one value per block).
+template <typename X, typename Op>
+__device__ __forceinline__ X row_reduce(X x, Op op, X *scratch, X *slot) {
+    x = block_reduce(x, op, scratch);
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned blocks = cluster.num_blocks();
+    if (blocks == 1) return x;
+    if (threadIdx.x == 0) *slot = x;
+    cluster.sync();
+    X r = *cluster.map_shared_rank(slot, 0);
+    for (unsigned b = 1; b < blocks; ++b) r = op(r, *cluster.map_shared_rank(slot, b));
+    cluster.sync();   // every block has read before a slot is written again
+    return r;
+}
+
 __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
                                               uint32_t out[4]) {
 #pragma unroll
@@ -105,11 +127,135 @@ __device__ __forceinline__ float gumbel_of_word(uint32_t x) {
     return -logf(e);
 }
 
+// Shared memory of the threshold search: a histogram of 256 bins per warp (counts, and tempered
+// masses in fixed point: integer sums do not depend on the order the atomics land in, so the search
+// gives the same threshold on every run), and the block's totals, which the cluster's other blocks read.
+struct RadixSmem {
+    uint32_t cnt[32][256];
+    unsigned long long mass[32][256];
+    uint32_t tcnt[256];
+    unsigned long long tmass[256];
+    uint32_t sel, above_cnt;
+    unsigned long long above_mass, target;
+};
+constexpr float MASS_ONE = 1099511627776.0f;   // 2^40: a weight in (0, 1] as an integer
+
+// The largest key T such that the tokens with key >= T (and >= floor_key) number at least `k`
+// (MASS false), or hold at least p of the tempered mass of all tokens >= floor_key, and are at
+// least one (MASS true): a radix search, eight bits of the key per pass from the top, in which only
+// the tokens that share the bits found so far are looked at again.  Masked tokens count as -inf
+// for top-k (they sort last, as in the reference) and take no part in the masses.
+template <typename T, bool MASS>
+__device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint32_t *bits, int tid, int TS, float m, uint32_t floor_key,
+                                    RadixSmem &sm) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int blocks = (int)cluster.num_blocks();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t key_ninf = Key<T>::of(Num<T>::from_f32(-INFINITY));
+    uint32_t prefix = 0, above_cnt = 0;
+    unsigned long long above_mass = 0, target = 0;
+    for (int level = 0; level < Key<T>::BITS / 8; ++level) {
+        const int shift = Key<T>::BITS - 8 * (level + 1);
+        for (int i = threadIdx.x; i < 32 * 256; i += ST) {
+            (&sm.cnt[0][0])[i] = 0;
+            if (MASS) (&sm.mass[0][0])[i] = 0;
+        }
+        __syncthreads();
+        for (int i = tid; i < a.v; i += TS) {
+            const bool gone = bits != nullptr && ((bits[i >> 5] >> (i & 31)) & 1u) != 0;
+            if (MASS && gone) continue;
+            const uint32_t key = gone ? key_ninf : Key<T>::of(z[i]);
+            if (key < floor_key) continue;
+            if (level > 0 && (key >> (shift + 8)) != prefix) continue;
+            const uint32_t d = (key >> shift) & 255u;
+            atomicAdd(&sm.cnt[warp][d], 1u);
+            if (MASS) atomicAdd(&sm.mass[warp][d], __float2ull_rn(expf(__fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau)) * MASS_ONE));
+        }
+        __syncthreads();
+        if (threadIdx.x < 256) {
+            uint32_t c = 0;
+            unsigned long long w = 0;
+            for (int x = 0; x < 32; ++x) {
+                c += sm.cnt[x][threadIdx.x];
+                if (MASS) w += sm.mass[x][threadIdx.x];
+            }
+            sm.tcnt[threadIdx.x] = c;
+            sm.tmass[threadIdx.x] = w;
+        }
+        if (blocks > 1) {
+            cluster.sync();
+            uint32_t c = 0;
+            unsigned long long w = 0;
+            if (threadIdx.x < 256) {
+                for (int r = 0; r < blocks; ++r) {
+                    c += *cluster.map_shared_rank(&sm.tcnt[threadIdx.x], r);
+                    if (MASS) w += *cluster.map_shared_rank(&sm.tmass[threadIdx.x], r);
+                }
+            }
+            cluster.sync();   // every block has read the others' totals
+            if (threadIdx.x < 256) { sm.tcnt[threadIdx.x] = c; sm.tmass[threadIdx.x] = w; }
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // Lane l holds bins 255 - 8 l down to 248 - 8 l: the higher bins on the lower lanes.
+            uint32_t c8 = 0;
+            unsigned long long w8 = 0;
+            for (int x = 0; x < 8; ++x) { c8 += sm.tcnt[255 - 8 * lane - x]; w8 += sm.tmass[255 - 8 * lane - x]; }
+            uint32_t c_before = c8;
+            unsigned long long w_before = w8;
+            for (int o = 1; o < 32; o <<= 1) {   // inclusive sums over the lanes up to this one
+                const uint32_t cu = __shfl_up_sync(0xffffffffu, c_before, o);
+                const unsigned long long wu = __shfl_up_sync(0xffffffffu, w_before, o);
+                if (lane >= o) { c_before += cu; w_before += wu; }
+            }
+            if (MASS && level == 0) {
+                const unsigned long long total = __shfl_sync(0xffffffffu, w_before, 31);
+                target = __double2ull_ru((double)a.p * (double)total);
+            }
+            uint32_t run_c = above_cnt + c_before - c8;
+            unsigned long long run_w = above_mass + w_before - w8;
+            int hit = -1;
+            uint32_t hit_c = 0;
+            unsigned long long hit_w = 0;
+            for (int x = 0; x < 8 && hit < 0; ++x) {
+                const int d = 255 - 8 * lane - x;
+                const uint32_t nc = run_c + sm.tcnt[d];
+                const unsigned long long nw = run_w + sm.tmass[d];
+                if (MASS ? (nw >= target && nc >= 1u) : (nc >= (uint32_t)a.top_k)) { hit = d; hit_c = run_c; hit_w = run_w; }
+                run_c = nc;
+                run_w = nw;
+            }
+            const unsigned vote = __ballot_sync(0xffffffffu, hit >= 0);
+            const int src = vote ? __ffs(vote) - 1 : 31;   // the lowest lane: the highest bin
+            if (lane == src) {
+                sm.sel = hit >= 0 ? (uint32_t)hit : 0u;
+                sm.above_cnt = hit >= 0 ? hit_c : run_c;
+                sm.above_mass = hit >= 0 ? hit_w : run_w;
+                sm.target = target;
+            }
+        }
+        __syncthreads();
+        prefix = (prefix << 8) | sm.sel;
+        above_cnt = sm.above_cnt;
+        above_mass = sm.above_mass;
+        target = sm.target;
+        __syncthreads();   // read before the next level writes
+    }
+    return prefix;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
     __shared__ float fs[32];
     __shared__ int is[32];
-    const int row = blockIdx.x, tid = threadIdx.x;
+    __shared__ float fslot;
+    __shared__ int islot;
+    extern __shared__ __align__(16) uint8_t radix_raw[];
+    RadixSmem &radix = *reinterpret_cast<RadixSmem *>(radix_raw);
+    cg::cluster_group cluster = cg::this_cluster();
+    const int blocks = (int)cluster.num_blocks();
+    const int row = blockIdx.x / blocks, tid = (int)cluster.block_rank() * ST + threadIdx.x;
+    const int TS = blocks * ST;   // the row's threads
     const T *z = static_cast<const T *>(a.logits) + (int64_t)row * a.stride;
     const uint32_t *bits = a.masked_bits;
     auto masked = [&](int i) { return bits != nullptr && ((bits[i >> 5] >> (i & 31)) & 1u) != 0; };
@@ -117,73 +263,40 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
 
     // 1. m = max over the unmasked tokens; 2. sum exp(z - m) (and, tempered, sum exp((z - m) tau)).
     float m = -INFINITY;
-    for (int i = tid; i < a.v; i += ST)
+    for (int i = tid; i < a.v; i += TS)
         if (!masked(i)) m = fmaxf(m, Num<T>::to_f32(z[i]));
-    m = block_reduce(m, MaxOp(), fs);
+    m = row_reduce(m, MaxOp(), fs, &fslot);
     const bool degenerate = m == -INFINITY;   // no finite unmasked logit: the lowest unmasked id, NaN
     const bool tempered_differs = !a.greedy && a.tau != 1.0f;
     float s1 = 0.f, wu = 0.f;
     int first = a.v;   // the lowest unmasked id holding the maximum
-    for (int i = tid; i < a.v; i += ST) {
+    for (int i = tid; i < a.v; i += TS) {
         if (masked(i)) continue;
         const float x = Num<T>::to_f32(z[i]);
         s1 += expf(x - m);
         if (tempered_differs) wu += expf((x - m) * a.tau);
         if (x == m && i < first) first = i;
     }
-    s1 = block_reduce(s1, AddOp(), fs);
-    if (tempered_differs) wu = block_reduce(wu, AddOp(), fs);
+    s1 = row_reduce(s1, AddOp(), fs, &fslot);
+    if (tempered_differs) wu = row_reduce(wu, AddOp(), fs, &fslot);
     const float lse = m + logf(s1);
 
     int token = 0;
     float tempered = 0.f, sampling = 0.f;
     bool own_tempered = true, own_sampling = true;   // false: the value is another output's (same bits)
     if (a.greedy || degenerate) {
-        token = block_reduce(first, MinOp(), is);
+        token = row_reduce(first, MinOp(), is, &islot);
     } else {
         // 3. The cuts: one threshold T on the keys; 0 keeps every token.
         uint32_t t_keep = 0;
         const bool cut = a.top_k > 0 || a.has_p;
-        if (a.top_k > 0) {
-            for (int bit = Key<T>::BITS - 1; bit >= 0; --bit) {
-                const uint32_t cand = t_keep | (1u << bit);
-                int count = 0;
-                for (int i = tid; i < a.v; i += ST) count += (masked(i) ? key_ninf : Key<T>::of(z[i])) >= cand ? 1 : 0;
-                count = block_reduce(count, AddOp(), is);
-                if (count >= a.top_k) t_keep = cand;
-            }
-        }
-        if (a.has_p) {
-            // The tempered mass of what top-k keeps, then the largest threshold whose mass reaches p of it.
-            float wk = 0.f;
-            for (int i = tid; i < a.v; i += ST)
-                if (!masked(i) && Key<T>::of(z[i]) >= t_keep) wk += expf((Num<T>::to_f32(z[i]) - m) * a.tau);
-            wk = block_reduce(wk, AddOp(), fs);
-            const float target = __fmul_rn(wk, a.p);
-            uint32_t t_p = 0;
-            for (int bit = Key<T>::BITS - 1; bit >= 0; --bit) {
-                const uint32_t cand = t_p | (1u << bit);
-                float mass = 0.f;
-                int any = 0;
-                for (int i = tid; i < a.v; i += ST) {
-                    if (masked(i)) continue;
-                    const uint32_t k = Key<T>::of(z[i]);
-                    if (k >= cand && k >= t_keep) {
-                        mass += expf((Num<T>::to_f32(z[i]) - m) * a.tau);
-                        any = 1;
-                    }
-                }
-                mass = block_reduce(mass, AddOp(), fs);
-                any = block_reduce(any, AddOp(), is);
-                if (any > 0 && mass >= target) t_p = cand;
-            }
-            t_keep = max(t_keep, t_p);
-        }
+        if (a.top_k > 0) t_keep = radix_threshold<T, false>(z, a, bits, tid, TS, m, 0u, radix);
+        if (a.has_p) t_keep = max(t_keep, radix_threshold<T, true>(z, a, bits, tid, TS, m, t_keep, radix));
 
         // 4. argmax of s + g over the kept tokens, ties to the lowest id; the kept tokens' mass.
         float best = -INFINITY, wp = 0.f;
         int best_i = a.v;
-        for (int g = tid; g < (a.v + 3) / 4; g += ST) {
+        for (int g = tid; g < (a.v + 3) / 4; g += TS) {
             uint32_t w[4];
             philox4x32_10((uint32_t)g, (uint32_t)row, a.off_lo, a.off_hi, a.key0, a.key1, w);
 #pragma unroll
@@ -198,7 +311,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
         }
         // (score, id) pairs: the larger score, then the lower id.
         {
-            const int lane = tid & 31, warp = tid >> 5;
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
             auto better = [](float sa, int ia, float sb, int ib) { return ib != INT_MAX && (ia == INT_MAX || sb > sa || (sb == sa && ib < ia)); };
             if (best_i == a.v) best_i = INT_MAX;
 #pragma unroll
@@ -218,14 +331,26 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
                 const int ib = __shfl_xor_sync(0xffffffffu, best_i, o);
                 if (better(best, best_i, sb, ib)) { best = sb; best_i = ib; }
             }
+            if (blocks > 1) {
+                if (threadIdx.x == 0) { fslot = best; islot = best_i; }
+                cluster.sync();
+                best = *cluster.map_shared_rank(&fslot, 0);
+                best_i = *cluster.map_shared_rank(&islot, 0);
+                for (int b = 1; b < blocks; ++b) {
+                    const float sb = *cluster.map_shared_rank(&fslot, b);
+                    const int ib = *cluster.map_shared_rank(&islot, b);
+                    if (better(best, best_i, sb, ib)) { best = sb; best_i = ib; }
+                }
+                cluster.sync();
+            }
         }
         token = best_i == INT_MAX ? 0 : best_i;
-        if (cut) wp = block_reduce(wp, AddOp(), fs);
+        if (cut) wp = row_reduce(wp, AddOp(), fs, &fslot);
         const float s_t = __fmul_rn(Num<T>::to_f32(z[token]) - m, a.tau);
         if (tempered_differs) tempered = s_t - logf(wu); else own_tempered = false;
         if (cut) sampling = s_t - logf(wp); else own_sampling = false;
     }
-    if (tid == 0) {
+    if (tid == 0) {   // the first thread of the row's first block
         const float logprob = Num<T>::to_f32(z[token]) - lse;
         if (!a.greedy || degenerate) {
             if (!own_tempered || degenerate) tempered = logprob;
@@ -242,15 +367,41 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
 
 }  // namespace
 
+template <typename T>
+static cudaError_t launch_t(const SampleArgs &a, int blocks, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(a.b * blocks), 1, 1);
+    cfg.blockDim = dim3(ST, 1, 1);
+    cfg.stream = stream;
+    cfg.dynamicSmemBytes = sizeof(RadixSmem);
+    cudaError_t e = cudaFuncSetAttribute(sample_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(RadixSmem));
+    if (e != cudaSuccess) return e;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)blocks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sample_kernel<T>, a);
+}
+
 cudaError_t launch_sample(int dtype, const SampleArgs &a, cudaStream_t stream, int *launches) {
     if (a.b == 0) return cudaSuccess;
+    // As many blocks to a row as fill the multiprocessors at this batch (one block of 1024 threads
+    // each), a power of two up to the portable cluster size; short rows take one.
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int blocks = 1;
+    while (blocks < 8 && (int64_t)a.b * blocks * 2 <= sms && a.v >= blocks * 2 * ST * 4) blocks *= 2;
+    cudaError_t e;
     switch (dtype) {
-        case 0: sample_kernel<float><<<a.b, ST, 0, stream>>>(a); break;
-        case 1: sample_kernel<__nv_bfloat16><<<a.b, ST, 0, stream>>>(a); break;
-        default: sample_kernel<__half><<<a.b, ST, 0, stream>>>(a); break;
+        case 0: e = launch_t<float>(a, blocks, stream); break;
+        case 1: e = launch_t<__nv_bfloat16>(a, blocks, stream); break;
+        default: e = launch_t<__half>(a, blocks, stream); break;
     }
     *launches += 1;
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace dash
