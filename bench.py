@@ -25,6 +25,7 @@ un-vendored crates and cannot be built here.
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import pathlib
@@ -220,6 +221,7 @@ def main():
     from dashmag_b200 import attention as A
     from dashmag_b200.contract import AttentionMask, AttentionOptions
     from dashmag_b200.rope import Rope
+    from dashmag_b200.sample import SampleOptions, sample
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the attention path has no CPU fallback")
@@ -369,6 +371,33 @@ def main():
                      "kernel": "rope_kernel (1 launch rotates Q and K)"},
     }
 
+    # ---- sampling the next token from the decoding step's logits ----
+    scfg = dict(b=DECODE["b"], v=151936)
+    zl = (torch.randn((scfg["b"], scfg["v"]), generator=torch.Generator(device=dev).manual_seed(3000 + rank), device=dev) * 3).to(torch.bfloat16)
+    sample_leg = {"workload": f"logits [{scfg['b']}, {scfg['v']}] bf16, N(0, 3): every token within reach of the draw (the worst case)"}
+    for name, so in (("plain", SampleOptions(seed=1)), ("t0.7_k50_p0.9", SampleOptions(temperature=0.7, top_k=50, top_p=0.9, seed=1))):
+        for _ in range(3):
+            sample(zl, so)
+        barrier()
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sreps = max(args.steps, 10)
+        sl0 = _lib.probe("kernel_launches")
+        q0.record()
+        for i in range(sreps):
+            sample(zl, dataclasses.replace(so, offset=i))
+        q1.record()
+        barrier()
+        s_ms = max_over_ranks(q0.elapsed_time(q1) / sreps)
+        s_bytes = zl.numel() * 2
+        sample_leg[name] = {"ms_per_step": s_ms, "tokens_per_s": sum_over_ranks(scfg["b"]) / (s_ms * 1e-3),
+                            "gpu_launches_per_step": (_lib.probe("kernel_launches") - sl0) / sreps,
+                            # the logits are read from L2 after the first pass: the kernel is bound by the
+                            # generator's and the logarithms' instructions, not by HBM; the fraction says so
+                            "roofline": {"bound": "hbm", "achieved": s_bytes / (s_ms * 1e-3) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                                         "frac": s_bytes / (s_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
+                                         "kernel": "sample_kernel (1 launch, a cluster of blocks per row)"}}
+    del zl
+
     # ---- decoding leg ----
     decode = None
     if not args.skip_decode:
@@ -452,6 +481,7 @@ def main():
                                   "traffic": 1.71e9, "traffic_unit": "bytes per pass",
                                   "kernel": "backward pass: delta_rows + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
             "rope": rope_leg,
+            "sample": sample_leg,
             "decode": decode,
             "cpu_baseline": None if args.skip_cpu else cpu_baseline(),
         }

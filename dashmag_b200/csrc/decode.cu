@@ -387,6 +387,7 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
         T *dst = const_cast<T *>(lane < 16 ? kbase + (int64_t)pos * a.k.st : vbase + (int64_t)pos * a.v.st) + cp_chunk * 8;
         *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
     }
+    const int pos_it = (pos >= c0 && pos < c1) ? (pos - c0) / DM_KEYS : -1;   // the tile of the new row, if this chunk holds it
     auto issue = [&](int it) {
         if (it < iters) {
             const uint32_t dst = ring + (uint32_t)(it % DM_STAGES) * 2 * DM_TILE;
@@ -395,8 +396,10 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
                 const int row = cp_row0 + 2 * j, key = c0 + it * DM_KEYS + row;
                 const bool valid = key < c1;
                 const uint32_t at = (uint32_t)(row * 256 + ((cp_chunk ^ (row & 7)) << 4));
-                cp_async16(dst + at, (key == pos ? knew : kbase + (int64_t)(valid ? key : c0) * a.k.st) + cp_chunk * 8, valid);
-                cp_async16(dst + DM_TILE + at, (key == pos ? vnew : vbase + (int64_t)(valid ? key : c0) * a.v.st) + cp_chunk * 8, valid);
+                const T *kp = kbase + (int64_t)(valid ? key : c0) * a.k.st, *vp = vbase + (int64_t)(valid ? key : c0) * a.v.st;
+                if (it == pos_it && key == pos) { kp = knew; vp = vnew; }   // only the tile that holds the new row looks for it
+                cp_async16(dst + at, kp + cp_chunk * 8, valid);
+                cp_async16(dst + DM_TILE + at, vp + cp_chunk * 8, valid);
             }
         }
         cp_async_commit();  // always, so that the group count stays in step with the tiles

@@ -296,16 +296,29 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
         // 4. argmax of s + g over the kept tokens, ties to the lowest id; the kept tokens' mass.
         float best = -INFINITY, wp = 0.f;
         int best_i = a.v;
+        // g lies within [-3.13, 22.9] (the words' range), and the row's largest logit is always kept
+        // (s = 0), so a token more than 26.1 below it is never drawn: it adds to the mass and skips
+        // the generator and the logarithms.
         for (int g = tid; g < (a.v + 3) / 4; g += TS) {
+            float s4[4];
+            bool draw = false;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 4 * g + e;
+                s4[e] = -INFINITY;
+                if (i >= a.v || masked(i) || Key<T>::of(z[i]) < t_keep) continue;
+                s4[e] = __fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau);
+                if (cut) wp += expf(s4[e]);
+                draw = draw || s4[e] >= -26.1f;
+            }
+            if (!draw) continue;
             uint32_t w[4];
             philox4x32_10((uint32_t)g, (uint32_t)row, a.off_lo, a.off_hi, a.key0, a.key1, w);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = 4 * g + e;
-                if (i >= a.v || masked(i) || Key<T>::of(z[i]) < t_keep) continue;
-                const float s = __fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau);
-                if (cut) wp += expf(s);
-                const float score = __fadd_rn(s, gumbel_of_word(w[e]));
+                if (!(s4[e] >= -26.1f)) continue;
+                const float score = __fadd_rn(s4[e], gumbel_of_word(w[e]));
                 if (score > best || (score == best && i < best_i) || best_i == a.v) { best = score; best_i = i; }
             }
         }
