@@ -131,8 +131,10 @@ __device__ __forceinline__ float gumbel_of_word(uint32_t x) {
 // masses in fixed point: integer sums do not depend on the order the atomics land in, so the search
 // gives the same threshold on every run), and the block's totals, which the cluster's other blocks read.
 struct RadixSmem {
-    uint32_t cnt[32][256];
-    unsigned long long mass[32][256];
+    // 32 copies of each bin: copy c of bin d at [c / 4][d][c % 4]; a thread uses copy 4 (warp / 4) + lane % 4, so
+    // that the lanes of a warp that meet in one bin (16-bit logits crowd into a few top bytes) spread over four words.
+    uint32_t cnt[8][256][4];
+    unsigned long long mass[8][256][4];
     uint32_t tcnt[256];
     unsigned long long tmass[256];
     uint32_t sel, above_cnt;
@@ -157,8 +159,8 @@ __device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint3
     for (int level = 0; level < Key<T>::BITS / 8; ++level) {
         const int shift = Key<T>::BITS - 8 * (level + 1);
         for (int i = threadIdx.x; i < 32 * 256; i += ST) {
-            (&sm.cnt[0][0])[i] = 0;
-            if (MASS) (&sm.mass[0][0])[i] = 0;
+            (&sm.cnt[0][0][0])[i] = 0;
+            if (MASS) (&sm.mass[0][0][0])[i] = 0;
         }
         __syncthreads();
         for (int i = tid; i < a.v; i += TS) {
@@ -168,16 +170,16 @@ __device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint3
             if (key < floor_key) continue;
             if (level > 0 && (key >> (shift + 8)) != prefix) continue;
             const uint32_t d = (key >> shift) & 255u;
-            atomicAdd(&sm.cnt[warp][d], 1u);
-            if (MASS) atomicAdd(&sm.mass[warp][d], __float2ull_rn(expf(__fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau)) * MASS_ONE));
+            atomicAdd(&sm.cnt[warp >> 2][d][lane & 3], 1u);
+            if (MASS) atomicAdd(&sm.mass[warp >> 2][d][lane & 3], __float2ull_rn(expf(__fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau)) * MASS_ONE));
         }
         __syncthreads();
         if (threadIdx.x < 256) {
             uint32_t c = 0;
             unsigned long long w = 0;
             for (int x = 0; x < 32; ++x) {
-                c += sm.cnt[x][threadIdx.x];
-                if (MASS) w += sm.mass[x][threadIdx.x];
+                c += sm.cnt[x >> 2][threadIdx.x][x & 3];
+                if (MASS) w += sm.mass[x >> 2][threadIdx.x][x & 3];
             }
             sm.tcnt[threadIdx.x] = c;
             sm.tmass[threadIdx.x] = w;
