@@ -43,9 +43,16 @@ namespace {
 
 constexpr int BM = 128;          // queries per block
 constexpr int BN = 128;          // keys per tile
-constexpr int HD = 128;          // head dimension
-constexpr int TILE_BYTES = BM * HD * 2;  // 32 KiB: any of the Q, K, V, P tiles
-constexpr int HALF_BYTES = TILE_BYTES / 2;  // one 64-column half: 128 rows of 128 bytes
+constexpr int HALF_BYTES = 128 * 128;  // one 64-column part of a tile: 128 rows of 128 bytes, what one TMA box brings
+// Head dimension HD = 128, or 256 (this kernel only: two accumulators of 256 columns do not fit the
+// two-tile kernel's tensor memory): a tile is HD / 64 parts, 32 KiB at 128, and at 256 the K and V
+// rings have one stage each (Q + K + V = 192 KiB).
+template <int HD> struct Geo1 {
+    static constexpr int PARTS = HD / 64;
+    static constexpr int TILE_BYTES = PARTS * HALF_BYTES;
+    static constexpr int NS = HD > 128 ? 1 : 2;
+    static constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (1 + 2 * NS) * TILE_BYTES /*Q, K ring, V ring*/ + 1024 /*Shared*/;
+};
 constexpr int THREADS = 224;
 constexpr float RESCALE_LOG2 = 8.0f;
 
@@ -61,7 +68,6 @@ struct Shared {
     unsigned int abort;
 };
 
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + 5 * TILE_BYTES /*Q, 2 K, 2 V*/ + 1024 /*Shared*/;
 
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
@@ -81,16 +87,17 @@ template <> struct Pack<__half> {
 
 }  // namespace
 
-template <typename T>
+template <typename T, int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Sm100FwdArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int PARTS = Geo1<HD>::PARTS, TILE_BYTES = Geo1<HD>::TILE_BYTES, NS = Geo1<HD>::NS;
     uint8_t *q_s = smem;
     uint8_t *k_s = q_s + TILE_BYTES;
-    uint8_t *v_s = k_s + 2 * TILE_BYTES;
-    Shared &sh = *reinterpret_cast<Shared *>(v_s + 2 * TILE_BYTES);
+    uint8_t *v_s = k_s + NS * TILE_BYTES;
+    Shared &sh = *reinterpret_cast<Shared *>(v_s + NS * TILE_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x;
@@ -152,15 +159,15 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // ---------------- TMA producer ----------------
         if (lane == 0 && n_tiles > 0) {
             mbar_expect_tx(q_full, TILE_BYTES);
-            tma_load_4d(smem_u32(q_s), &tm_q, q_full, 0, h, m0, b);
-            tma_load_4d(smem_u32(q_s + HALF_BYTES), &tm_q, q_full, 64, h, m0, b);
+#pragma unroll
+            for (int part = 0; part < PARTS; ++part) tma_load_4d(smem_u32(q_s + part * HALF_BYTES), &tm_q, q_full, 64 * part, h, m0, b);
             for (int j = 0; j < n_tiles && !failed; ++j) {
-                const int st = j & 1, ph = (j >> 1) & 1, k0 = kmin + j * BN;
+                const int st = j % NS, ph = (j / NS) & 1, k0 = kmin + j * BN;
                 if (!mbar_wait(BAR(sh.bar.k_empty, st), ph ^ 1)) { failed = true; break; }
                 uint32_t full = BAR(sh.bar.k_full, st), dst = smem_u32(k_s + st * TILE_BYTES);
                 mbar_expect_tx(full, TILE_BYTES);
-                tma_load_4d(dst, &tm_k, full, 0, hk, k0, b);
-                tma_load_4d(dst + HALF_BYTES, &tm_k, full, 64, hk, k0, b);
+#pragma unroll
+                for (int part = 0; part < PARTS; ++part) tma_load_4d(dst + part * HALF_BYTES, &tm_k, full, 64 * part, hk, k0, b);
             }
         }
     } else if (warp == 6) {
@@ -168,12 +175,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // before the V tile of the same keys, and neither load should queue behind the other) ----
         if (lane == 0 && n_tiles > 0) {
             for (int j = 0; j < n_tiles && !failed; ++j) {
-                const int st = j & 1, ph = (j >> 1) & 1, k0 = kmin + j * BN;
+                const int st = j % NS, ph = (j / NS) & 1, k0 = kmin + j * BN;
                 if (!mbar_wait(BAR(sh.bar.v_empty, st), ph ^ 1)) { failed = true; break; }
                 const uint32_t full = BAR(sh.bar.v_full, st), dst = smem_u32(v_s + st * TILE_BYTES);
                 mbar_expect_tx(full, TILE_BYTES);
-                tma_load_4d(dst, &tm_v, full, 0, hk, k0, b);
-                tma_load_4d(dst + HALF_BYTES, &tm_v, full, 64, hk, k0, b);
+#pragma unroll
+                for (int part = 0; part < PARTS; ++part) tma_load_4d(dst + part * HALF_BYTES, &tm_v, full, 64 * part, hk, k0, b);
             }
         }
     } else if (warp == 1) {
@@ -183,15 +190,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // A = P K-major, B = V MN-major
             const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s), 16, 1024);
             auto issue_pv = [&](int i) -> bool {
-                const int st = i & 1, ph = (i >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full, st), ph) && mbar_wait(BAR(sh.bar.p_full, st), ph)))
+                const int st = i & 1, ph = (i >> 1) & 1;         // the S / P buffer of the tile
+                const int vst = i % NS, vph = (i / NS) & 1;     // its V stage
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full, vst), vph) && mbar_wait(BAR(sh.bar.p_full, st), ph)))
                     return false;
                 tc_fence_after_sync();
                 // A = P: 16 keys = 32 bytes along the swizzled row, the second 64 keys in the second half.
                 // B = V: rows are keys (K of this product), 128 bytes of head dimension per row and half:
                 // 64-column atoms HALF_BYTES apart (leading), 8-key groups 1024 bytes apart.
-                const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * TILE_BYTES), HALF_BYTES, 1024);
-                const uint32_t v_empty = BAR(sh.bar.v_empty, st), s_empty = BAR(sh.bar.s_empty, st);
+                const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + vst * TILE_BYTES), HALF_BYTES, 1024);
+                const uint32_t v_empty = BAR(sh.bar.v_empty, vst), s_empty = BAR(sh.bar.s_empty, st);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < BN / 16; ++ks)
@@ -208,13 +216,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (!__all_sync(0xffffffffu, mbar_wait(q_full, 0))) failed = true;
             for (int j = 0; j < n_tiles && !failed; ++j) {
                 const int st = j & 1, ph = (j >> 1) & 1;
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full, st), ph) && mbar_wait(BAR(sh.bar.s_empty, st), ph ^ 1))) {
+                const int kst = j % NS, kph = (j / NS) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full, kst), kph) && mbar_wait(BAR(sh.bar.s_empty, st), ph ^ 1))) {
                     failed = true;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + st * TILE_BYTES), 16, 1024);
-                const uint32_t k_empty = BAR(sh.bar.k_empty, st), s_full = BAR(sh.bar.s_full, st);
+                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + kst * TILE_BYTES), 16, 1024);
+                const uint32_t k_empty = BAR(sh.bar.k_empty, kst), s_full = BAR(sh.bar.s_full, st);
                 if (elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < HD / 16; ++ks) {
@@ -313,8 +322,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (!__all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1))) { failed = true; break; }
                 if (__any_sync(0xffffffffu, rescale)) {
                     tc_fence_after_sync();
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
                         uint32_t o[32];
                         tmem_ld32(t_lane + 256 + c * 32, o);
                         tmem_ld_wait();
@@ -341,14 +350,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (row < a.tq && !failed) {
                 uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int c = 0; c < 16; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
+                for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
                 a.lse[base] = -INFINITY;
             }
         } else if (__all_sync(0xffffffffu, mbar_wait(o_ready, (n_tiles - 1) & 1))) {
             tc_fence_after_sync();
             const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
                 tmem_ld32(t_lane + 256 + c * 32, o);
                 tmem_ld_wait();
@@ -382,20 +391,25 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
 }
 
+namespace {
+template <typename T, int HD>
+cudaError_t launch_fwd_t(dim3 grid, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv, const Sm100FwdArgs &a,
+                         cudaStream_t stream) {
+    constexpr size_t smem = Geo1<HD>::SMEM_BYTES;
+    cudaError_t e = cudaFuncSetAttribute(fwd_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    fwd_sm100_kernel<T, HD><<<grid, THREADS, smem, stream>>>(tq, tk, tv, a);
+    return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                              const Sm100FwdArgs &a, cudaStream_t stream) {
     dim3 grid(a.hq, (a.tq + BM - 1) / BM, a.b);
-    cudaError_t e;
-    if (dtype == DASH_ATTN_BF16) {
-        e = cudaFuncSetAttribute(fwd_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        fwd_sm100_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
-    } else {
-        e = cudaFuncSetAttribute(fwd_sm100_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        fwd_sm100_kernel<__half><<<grid, THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a);
-    }
-    return cudaGetLastError();
+    if (dtype == DASH_ATTN_BF16)
+        return a.d == 256 ? launch_fwd_t<__nv_bfloat16, 256>(grid, tq, tk, tv, a, stream)
+                          : launch_fwd_t<__nv_bfloat16, 128>(grid, tq, tk, tv, a, stream);
+    return a.d == 256 ? launch_fwd_t<__half, 256>(grid, tq, tk, tv, a, stream) : launch_fwd_t<__half, 128>(grid, tq, tk, tv, a, stream);
 }
 
 cudaError_t read_sm100_status(unsigned int *status, bool clear) {

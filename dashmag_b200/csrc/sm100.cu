@@ -95,7 +95,10 @@ bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const 
     // tile of queries or of keys (one block per head), the tensor cores gain nothing, and the generic
     // kernels' f32 FMA sums keep the log-sum-exp within the one or two units in the last place that
     // the reference's records allow at those sizes.
-    if (p->d != 128 && !(p->d == 64 && p->tq >= 128 && p->tk >= 128)) return false;
+    // Head dimension 256: the one-tile forward only (two accumulators of 256 columns are all of tensor
+    // memory, so the backward stays on the generic kernels), under the same size rule.
+    const bool big = p->tq >= 128 && p->tk >= 128;
+    if (p->d != 128 && !(p->d == 64 && big) && !(p->d == 256 && big && !backward)) return false;
     const float scale = resolved_scale(p);
     if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
     if (!q || !k || !v) return false;
@@ -132,7 +135,7 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
     f.lse = a.lse;
     f.mask = a.mask;
     f.pair_heads = ((p->hq / p->hkv) % 2 == 0) ? 1 : 0;
-    cudaError_t e = (one_tile && p->d == 128) ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, to, f, stream);
+    cudaError_t e = ((one_tile && p->d == 128) || p->d == 256) ? launch_fwd_sm100(p->dtype, tq, tk, tv, f, stream) : launch_fwd2_sm100(p->dtype, tq, tk, tv, to, f, stream);
     *launches += 1;
     return e;
 }
