@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
 }
 
 // ---------------------------------------------------------------------------------------------
-// The split pass on the tensor cores (16-bit cache, head dimension 128, groups of up to 16 heads)
+// The split pass on the tensor cores (16-bit cache, head dimension 128 or 64, groups of up to 16 heads)
 // ---------------------------------------------------------------------------------------------
 // With four or more query heads to a key-value head the scalar pass spends its time on FMA issue,
 // not on HBM: a cache row of 512 bytes feeds 2048 multiply-adds.  Here the query heads of the group
@@ -299,12 +299,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
 // N tiles, then O += P V with P taken straight from the accumulator registers of S as the A
 // operand.  One warp per (chunk, key-value head) as before, with a ring of its own in shared memory:
 // every lane copies 16-byte pieces of the tile's 16 key rows and 16 value rows asynchronously, two
-// tiles ahead, into 256-byte rows whose 16-byte chunks are XOR-swizzled by the row, and ldmatrix
+// tiles ahead, into rows (256 bytes at D = 128) whose 16-byte chunks are XOR-swizzled by the row, and ldmatrix
 // reads the fragments from there without bank conflicts (transposed for V).
 constexpr int DM_WARPS = 8;     // warps per block
 constexpr int DM_STAGES = 3;    // tiles of the per-warp ring
 constexpr int DM_KEYS = 16;     // keys per tile
-constexpr int DM_TILE = DM_KEYS * 256;   // bytes of a K (or V) tile: 16 rows of 128 16-bit values
 
 template <typename T> struct MmaType;
 template <> struct MmaType<__nv_bfloat16> {
@@ -338,9 +337,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeArgs a) {
-    constexpr int D = 128;
+    constexpr int ROWB = 2 * D;                 // bytes of a cache row: 256 at D = 128, 128 at D = 64
+    constexpr int CH = D / 8;                   // its 16-byte chunks
+    constexpr int DM_TILE = DM_KEYS * ROWB;     // bytes of a K (or V) tile of 16 rows
     extern __shared__ __align__(128) uint8_t dm_ring[];   // [warp][stage][K tile | V tile]
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int group = a.hq / a.hkv;
@@ -376,15 +377,16 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(dm_ring)) + (uint32_t)wib * DM_STAGES * 2 * DM_TILE;
 
     // This lane's pieces of a tile: chunk (lane % 16) of rows (lane / 16) + 2 j.
-    const int cp_chunk = lane & 15, cp_row0 = lane >> 4;
+    const int cp_chunk = lane % CH, cp_row0 = lane / CH;
+    constexpr int RPP = 32 / CH;                // rows the warp copies per pass
     // The appending step: the row at `pos` comes from the new rows, and the warp whose chunk holds
-    // it also writes it into the cache (sixteen lanes the key row, sixteen the value row).
+    // it also writes it into the cache (D / 8 lanes the key row, D / 8 the value row).
     const int pos = decode_append_at(a, b);
     const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * D;
     const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * D;
-    if (pos >= c0 && pos < c1) {
-        const T *src = (lane < 16 ? knew : vnew) + cp_chunk * 8;
-        T *dst = const_cast<T *>(lane < 16 ? kbase + (int64_t)pos * a.k.st : vbase + (int64_t)pos * a.v.st) + cp_chunk * 8;
+    if (pos >= c0 && pos < c1 && lane < 2 * CH) {
+        const T *src = (lane < CH ? knew : vnew) + cp_chunk * 8;
+        T *dst = const_cast<T *>(lane < CH ? kbase + (int64_t)pos * a.k.st : vbase + (int64_t)pos * a.v.st) + cp_chunk * 8;
         *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
     }
     const int pos_it = (pos >= c0 && pos < c1) ? (pos - c0) / DM_KEYS : -1;   // the tile of the new row, if this chunk holds it
@@ -392,10 +394,10 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
         if (it < iters) {
             const uint32_t dst = ring + (uint32_t)(it % DM_STAGES) * 2 * DM_TILE;
 #pragma unroll
-            for (int j = 0; j < DM_KEYS / 2; ++j) {
-                const int row = cp_row0 + 2 * j, key = c0 + it * DM_KEYS + row;
+            for (int j = 0; j < DM_KEYS / RPP; ++j) {
+                const int row = cp_row0 + RPP * j, key = c0 + it * DM_KEYS + row;
                 const bool valid = key < c1;
-                const uint32_t at = (uint32_t)(row * 256 + ((cp_chunk ^ (row & 7)) << 4));
+                const uint32_t at = (uint32_t)(row * ROWB + ((cp_chunk ^ (row & 7)) << 4));
                 const T *kp = kbase + (int64_t)(valid ? key : c0) * a.k.st, *vp = vbase + (int64_t)(valid ? key : c0) * a.v.st;
                 if (it == pos_it && key == pos) { kp = knew; vp = vnew; }   // only the tile that holds the new row looks for it
                 cp_async16(dst + at, kp + cp_chunk * 8, valid);
@@ -431,7 +433,7 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
 #pragma unroll
             for (int ks = 0; ks < D / 16; ks += 2) {
                 uint32_t kb[4];   // b0, b1 of k-step ks, then of ks + 1
-                ldmatrix_x4(kt + (uint32_t)(row * 256 + (((2 * ks + lm) ^ (row & 7)) << 4)), kb);
+                ldmatrix_x4(kt + (uint32_t)(row * ROWB + (((2 * ks + lm) ^ (row & 7)) << 4)), kb);
                 MmaType<T>::mma(sc[nt], qa[ks], kb[0], kb[1]);
                 MmaType<T>::mma(sc[nt], qa[ks + 1], kb[2], kb[3]);
             }
@@ -476,7 +478,7 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
         for (int n = 0; n < D / 8; n += 2) {
             uint32_t vb[4];   // b0, b1 of d-tile n, then of n + 1
             const int row = (lm & 1) * 8 + lr, chunk = n + (lm >> 1);
-            ldmatrix_x4_trans(vt + (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4)), vb);
+            ldmatrix_x4_trans(vt + (uint32_t)(row * ROWB + ((chunk ^ (row & 7)) << 4)), vb);
             MmaType<T>::mma(o[n], pa, vb[0], vb[1]);
             MmaType<T>::mma(o[n], pl, vb[0], vb[1]);
             MmaType<T>::mma(o[n + 1], pa, vb[2], vb[3]);
@@ -644,18 +646,18 @@ static cudaError_t split_vec(const DecodeArgs &a, cudaStream_t stream) {
     return split_vec_g<T, D, 1>(a, grid, stream);
 }
 
-template <typename T>
+template <typename T, int D>
 static cudaError_t split_mma(const DecodeArgs &a, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE;
-    cudaError_t e = cudaFuncSetAttribute(decode_split_mma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    constexpr size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_KEYS * 2 * D;
+    cudaError_t e = cudaFuncSetAttribute(decode_split_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const long long units = (long long)a.splits * a.hkv;
     dim3 grid((unsigned)((units + DM_WARPS - 1) / DM_WARPS), a.b);
-    decode_split_mma_kernel<T><<<grid, DM_WARPS * 32, smem, stream>>>(a);
+    decode_split_mma_kernel<T, D><<<grid, DM_WARPS * 32, smem, stream>>>(a);
     return cudaGetLastError();
 }
-template <>
-cudaError_t split_mma<float>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }   // never taken: 16-bit caches only
+template <> cudaError_t split_mma<float, 128>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }   // never taken: 16-bit caches only
+template <> cudaError_t split_mma<float, 64>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }
 
 // DASH_ATTN_DECODE_MMA=0 keeps the FMA pass (for comparison runs).
 static bool decode_force_scalar_pass() {
@@ -666,7 +668,9 @@ static bool decode_force_scalar_pass() {
 template <typename T>
 static cudaError_t decode_t(const DecodeArgs &a, bool vector_ok, cudaStream_t stream, int *launches) {
     cudaError_t e;
-    if (vector_ok && sizeof(T) == 2 && a.d == 128 && a.hq / a.hkv >= 4 && a.hq / a.hkv <= 16 && !decode_force_scalar_pass()) e = split_mma<T>(a, stream);
+    const bool mma = vector_ok && sizeof(T) == 2 && a.hq / a.hkv >= 4 && a.hq / a.hkv <= 16 && !decode_force_scalar_pass();
+    if (mma && a.d == 128) e = split_mma<T, 128>(a, stream);
+    else if (mma && a.d == 64) e = split_mma<T, 64>(a, stream);
     else if (vector_ok && a.d == 64) e = split_vec<T, 64>(a, stream);
     else if (vector_ok && a.d == 128) e = split_vec<T, 128>(a, stream);
     else if (vector_ok && a.d == 256) e = split_vec<T, 256>(a, stream);

@@ -22,6 +22,8 @@ CASES = [
     ("tensor-core pass, window", [3, 16, 2, 1300, 128], [1299, 600, 40], 100),
     ("full cache takes no row", [3, 8, 2, 300, 128], [300, 1000, 299], None),
     ("FMA pass: D64", [4, 4, 2, 333, 64], [0, 332, 100, 15], None),
+    ("tensor-core pass: D64, group 8", [3, 16, 2, 700, 64], [699, 0, 350], None),
+    ("tensor-core pass: D64, window", [2, 8, 2, 1300, 64], [1299, 40], 100),
     ("FMA pass: group 2, D128", [2, 4, 2, 520, 128], [519, 77], 64),
     ("scalar pass: odd head dimension", [2, 4, 2, 90, 40], [89, 30], 10),
 ]

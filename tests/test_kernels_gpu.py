@@ -220,6 +220,10 @@ def decode_cases():
         ("group of 16, D128", [2, 32, 2, 300, 128], [300, 123], None),
         ("group of 12, D128, window", [3, 24, 2, 1100, 128], [1100, 17, 600], 500),
         ("group of 4, D128, long", [2, 8, 2, 5000, 128], [4999, 2500], None),
+        # the same pass at head dimension 64
+        ("group of 4, D64, long", [2, 8, 2, 5000, 64], [4999, 2500], None),
+        ("group of 16, D64, window", [3, 32, 2, 1100, 64], [1100, 17, 600], 500),
+        ("group of 6, D64", [2, 12, 2, 333, 64], [333, 1], None),
     ]
 
 
