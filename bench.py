@@ -473,12 +473,14 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": fwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": fwd_tf / tensor_peak, "frac_of_nominal_2250": fwd_tf / 2250.0,
+                         "frac_of_sustained_peak": fwd_tf / pk["tensor_sustained"],
                          "peak_source": pk["source"] + " burst (kernel timed alone)",
                          # dram read + write of one launch, ncu capture of this workload (profiles/fwd2_sm100_config2.md)
                          "traffic": 307.8e6, "traffic_unit": "bytes per launch",
                          "kernel": "fwd2_sm100_kernel (1 launch per pass)"},
             "roofline_backward": {"bound": "tensor", "achieved": bwd_tf, "peak": tensor_peak, "unit": "TFLOP/s",
                                   "frac": bwd_tf / tensor_peak, "frac_of_nominal_2250": bwd_tf / 2250.0,
+                                  "frac_of_sustained_peak": bwd_tf / pk["tensor_sustained"],
                                   # delta 0.27 GB + dq 0.45 GB + dkdv 0.99 GB (profiles/bwd_*_config2.md)
                                   "traffic": 1.71e9, "traffic_unit": "bytes per pass",
                                   "kernel": "backward pass: delta_rows + bwd_dq_sm100 + bwd_plan + bwd_dkdv_sm100"},
