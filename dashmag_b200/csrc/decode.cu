@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
 }
 
 // ---------------------------------------------------------------------------------------------
-// The split pass on the tensor cores (16-bit cache, head dimension 128 or 64, groups of up to 16 heads)
+// The split pass on the tensor cores (16-bit cache, head dimension 64, 128 or 256, groups of up to 16 heads)
 // ---------------------------------------------------------------------------------------------
 // With four or more query heads to a key-value head the scalar pass spends its time on FMA issue,
 // not on HBM: a cache row of 512 bytes feeds 2048 multiply-adds.  Here the query heads of the group
@@ -337,16 +337,23 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-template <typename T, int D>
+// PARTS = 2 (head dimension 256): two neighbouring warps share a unit, each with D = 128 of the 256
+// features - its half of the scores' sum over the features, which the two exchange through shared
+// memory and add (in one order, so both hold the same bits), its half of Q, of every K and V row
+// and of the output; the accumulators of a whole row of 256 would not fit a thread's registers.
+template <typename T, int D, int PARTS>
 __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeArgs a) {
-    constexpr int ROWB = 2 * D;                 // bytes of a cache row: 256 at D = 128, 128 at D = 64
+    constexpr int DFULL = D * PARTS;            // the head dimension; D is what one warp takes of it
+    constexpr int ROWB = 2 * D;                 // bytes of a warp's part of a cache row: 256 at D = 128, 128 at D = 64
     constexpr int CH = D / 8;                   // its 16-byte chunks
     constexpr int DM_TILE = DM_KEYS * ROWB;     // bytes of a K (or V) tile of 16 rows
-    extern __shared__ __align__(128) uint8_t dm_ring[];   // [warp][stage][K tile | V tile]
+    extern __shared__ __align__(128) uint8_t dm_ring[];   // [warp][stage][K tile | V tile], then the warps' score exchange
+    float *dm_exchange = reinterpret_cast<float *>(dm_ring + (size_t)DM_WARPS * DM_STAGES * 2 * DM_KEYS * ROWB);   // [warp][lane][8]
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int group = a.hq / a.hkv;
     const int b = blockIdx.y;
-    const long long unit = (long long)blockIdx.x * DM_WARPS + wib;
+    const long long unit = ((long long)blockIdx.x * DM_WARPS + wib) / PARTS;
+    const int part = wib % PARTS, d0 = part * D;   // this warp's features [d0, d0 + D)
     const int hk = (int)(unit % a.hkv);
     const long long split = unit / a.hkv;
     if (split >= a.splits) return;
@@ -361,8 +368,8 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     // Q as the A operand of every score MMA: [16 heads x 16 d] per k-step, rows past the group zero.
     uint32_t qa[D / 16][4];
     {
-        const T *q0 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g, group - 1)) * a.q_sh;
-        const T *q1 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g + 8, group - 1)) * a.q_sh;
+        const T *q0 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g, group - 1)) * a.q_sh + d0;
+        const T *q1 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g + 8, group - 1)) * a.q_sh + d0;
         const bool live0 = g < group, live1 = g + 8 < group;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -372,8 +379,8 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
             qa[ks][3] = live1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8 + 2 * t) : 0u;
         }
     }
-    const T *kbase = static_cast<const T *>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)hk * a.k.sh;
-    const T *vbase = static_cast<const T *>(a.v.ptr) + (int64_t)b * a.v.sb + (int64_t)hk * a.v.sh;
+    const T *kbase = static_cast<const T *>(a.k.ptr) + (int64_t)b * a.k.sb + (int64_t)hk * a.k.sh + d0;
+    const T *vbase = static_cast<const T *>(a.v.ptr) + (int64_t)b * a.v.sb + (int64_t)hk * a.v.sh + d0;
     const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(dm_ring)) + (uint32_t)wib * DM_STAGES * 2 * DM_TILE;
 
     // This lane's pieces of a tile: chunk (lane % 16) of rows (lane / 16) + 2 j.
@@ -382,8 +389,8 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     // The appending step: the row at `pos` comes from the new rows, and the warp whose chunk holds
     // it also writes it into the cache (D / 8 lanes the key row, D / 8 the value row).
     const int pos = decode_append_at(a, b);
-    const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * D;
-    const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * D;
+    const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * DFULL + d0;
+    const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * DFULL + d0;
     if (pos >= c0 && pos < c1 && lane < 2 * CH) {
         const T *src = (lane < CH ? knew : vnew) + cp_chunk * 8;
         T *dst = const_cast<T *>(lane < CH ? kbase + (int64_t)pos * a.k.st : vbase + (int64_t)pos * a.v.st) + cp_chunk * 8;
@@ -437,6 +444,23 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
                 MmaType<T>::mma(sc[nt], qa[ks], kb[0], kb[1]);
                 MmaType<T>::mma(sc[nt], qa[ks + 1], kb[2], kb[3]);
             }
+        }
+        if constexpr (PARTS == 2) {
+            // The other half of the sum over the features is the neighbouring warp's: both write theirs, meet,
+            // and add part 0's and part 1's in that order.
+            float *mine = dm_exchange + ((size_t)wib * 32 + lane) * 8, *other = dm_exchange + ((size_t)(wib ^ 1) * 32 + lane) * 8;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+                *reinterpret_cast<float4 *>(mine + 4 * nt) = make_float4(sc[nt][0], sc[nt][1], sc[nt][2], sc[nt][3]);
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (wib >> 1)) : "memory");
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const float4 o4 = *reinterpret_cast<const float4 *>(other + 4 * nt);
+                const float theirs[4] = {o4.x, o4.y, o4.z, o4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nt][e] = part == 0 ? sc[nt][e] + theirs[e] : theirs[e] + sc[nt][e];
+            }
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + (wib >> 1)) : "memory");   // both have read before the next tile's are written
         }
         // Online softmax of rows g (values 0, 1 of a tile) and g + 8 (values 2, 3); a tile's columns
         // are keys key0 + 8 nt + 2 t + {0, 1}.
@@ -496,11 +520,11 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
         if (hg < group) {
             const int h = hk * group + hg;
             const float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
-            float *po = a.part_o + (((int64_t)b * a.hq + h) * a.splits + split) * D + 2 * t;
+            float *po = a.part_o + (((int64_t)b * a.hq + h) * a.splits + split) * DFULL + d0 + 2 * t;
 #pragma unroll
             for (int n = 0; n < D / 8; ++n)
                 *reinterpret_cast<float2 *>(po + n * 8) = make_float2(o[n][2 * rr] * inv, o[n][2 * rr + 1] * inv);
-            if (t == 0) a.part_lse[((int64_t)b * a.hq + h) * a.splits + split] = l[rr] > 0.f ? m[rr] * a.scale + __logf(l[rr]) : -INFINITY;
+            if (t == 0 && part == 0) a.part_lse[((int64_t)b * a.hq + h) * a.splits + split] = l[rr] > 0.f ? m[rr] * a.scale + __logf(l[rr]) : -INFINITY;
         }
     }
 }
@@ -646,18 +670,20 @@ static cudaError_t split_vec(const DecodeArgs &a, cudaStream_t stream) {
     return split_vec_g<T, D, 1>(a, grid, stream);
 }
 
-template <typename T, int D>
+template <typename T, int DFULL>
 static cudaError_t split_mma(const DecodeArgs &a, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_KEYS * 2 * D;
-    cudaError_t e = cudaFuncSetAttribute(decode_split_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    constexpr int PARTS = DFULL > 128 ? 2 : 1, D = DFULL / PARTS;
+    constexpr size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_KEYS * 2 * D + (PARTS == 2 ? (size_t)DM_WARPS * 32 * 8 * sizeof(float) : 0);
+    cudaError_t e = cudaFuncSetAttribute(decode_split_mma_kernel<T, D, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    const long long units = (long long)a.splits * a.hkv;
+    const long long units = (long long)a.splits * a.hkv * PARTS;
     dim3 grid((unsigned)((units + DM_WARPS - 1) / DM_WARPS), a.b);
-    decode_split_mma_kernel<T, D><<<grid, DM_WARPS * 32, smem, stream>>>(a);
+    decode_split_mma_kernel<T, D, PARTS><<<grid, DM_WARPS * 32, smem, stream>>>(a);
     return cudaGetLastError();
 }
 template <> cudaError_t split_mma<float, 128>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }   // never taken: 16-bit caches only
 template <> cudaError_t split_mma<float, 64>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }
+template <> cudaError_t split_mma<float, 256>(const DecodeArgs &, cudaStream_t) { return cudaErrorInvalidValue; }
 
 // DASH_ATTN_DECODE_MMA=0 keeps the FMA pass (for comparison runs).
 static bool decode_force_scalar_pass() {
@@ -671,6 +697,7 @@ static cudaError_t decode_t(const DecodeArgs &a, bool vector_ok, cudaStream_t st
     const bool mma = vector_ok && sizeof(T) == 2 && a.hq / a.hkv >= 4 && a.hq / a.hkv <= 16 && !decode_force_scalar_pass();
     if (mma && a.d == 128) e = split_mma<T, 128>(a, stream);
     else if (mma && a.d == 64) e = split_mma<T, 64>(a, stream);
+    else if (mma && a.d == 256) e = split_mma<T, 256>(a, stream);
     else if (vector_ok && a.d == 64) e = split_vec<T, 64>(a, stream);
     else if (vector_ok && a.d == 128) e = split_vec<T, 128>(a, stream);
     else if (vector_ok && a.d == 256) e = split_vec<T, 256>(a, stream);

@@ -224,6 +224,9 @@ def decode_cases():
         ("group of 4, D64, long", [2, 8, 2, 5000, 64], [4999, 2500], None),
         ("group of 16, D64, window", [3, 32, 2, 1100, 64], [1100, 17, 600], 500),
         ("group of 6, D64", [2, 12, 2, 333, 64], [333, 1], None),
+        # and at 256, a row's features over two warps
+        ("group of 16, D256, window", [2, 32, 2, 1100, 256], [1100, 600], 500),
+        ("group of 4, D256, long", [2, 4, 1, 5000, 256], [4999, 17], None),
     ]
 
 
