@@ -396,7 +396,9 @@ def main():
                             # the logits are read from L2 after the first pass: the kernel is bound by the
                             # generator's and the logarithms' instructions, not by HBM; the fraction says so
                             "roofline": {"bound": "hbm", "achieved": s_bytes / (s_ms * 1e-3) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
-                                         "frac": s_bytes / (s_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
+                                         "frac": s_bytes / (s_ms * 1e-3) / 1e9 / pk["hbm"],
+                                         # dram read of one launch = the logits once (profiles/sample_kernel_batch64.md)
+                                         "traffic": 19.53e6, "traffic_unit": "bytes per launch",
                                          "kernel": "sample_kernel (1 launch, a cluster of blocks per row)"}}
     del zl
 
