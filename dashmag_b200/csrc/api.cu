@@ -188,9 +188,13 @@ void decode_plan(const dash_attn_decode_params *p, int *chunk, int *splits) {
     if (const char *env = std::getenv("DASH_ATTN_DECODE_CHUNK")) {
         c = std::atoll(env);
     } else {
+        // Chunks of 128 to 512 keys, as long as they still leave units (a chunk of a key-value head;
+        // a group of more than sixteen query heads counts once per sixteen) to fill the warps of the GPU:
+        // under 128 keys a warp's set-up outweighs its tiles.
         const long long want = 148LL * 16 * 4;
-        long long per = (long long)p->s * p->b * p->hkv / want;
-        c = 64;
+        const long long head_blocks = p->hkv > 0 ? (p->hq / p->hkv + 15) / 16 : 1;
+        long long per = (long long)p->s * p->b * p->hkv * head_blocks / want;
+        c = 128;
         while (c * 2 <= per && c < 512) c *= 2;
     }
     if (c < 8) c = 8;

@@ -354,8 +354,13 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     const int b = blockIdx.y;
     const long long unit = ((long long)blockIdx.x * DM_WARPS + wib) / PARTS;
     const int part = wib % PARTS, d0 = part * D;   // this warp's features [d0, d0 + D)
-    const int hk = (int)(unit % a.hkv);
-    const long long split = unit / a.hkv;
+    // A unit: sixteen query heads of a group (the M rows of the MMAs; a group of more takes several
+    // units side by side, whose warps read the same chunk of the cache at the same time: once from
+    // HBM, the rest from L2), a key-value head, a chunk.
+    const int hblocks = (group + 15) / 16;
+    const int g_base = (int)(unit % hblocks) * 16;
+    const int hk = (int)((unit / hblocks) % a.hkv);
+    const long long split = unit / hblocks / a.hkv;
     if (split >= a.splits) return;
     int first, len;
     decode_range(a, b, first, len);
@@ -368,9 +373,9 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     // Q as the A operand of every score MMA: [16 heads x 16 d] per k-step, rows past the group zero.
     uint32_t qa[D / 16][4];
     {
-        const T *q0 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g, group - 1)) * a.q_sh + d0;
-        const T *q1 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g + 8, group - 1)) * a.q_sh + d0;
-        const bool live0 = g < group, live1 = g + 8 < group;
+        const T *q0 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g_base + g, group - 1)) * a.q_sh + d0;
+        const T *q1 = static_cast<const T *>(a.q) + (int64_t)b * a.q_sb + (int64_t)(hk * group + min(g_base + g + 8, group - 1)) * a.q_sh + d0;
+        const bool live0 = g_base + g < group, live1 = g_base + g + 8 < group;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
             qa[ks][0] = live0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 2 * t) : 0u;
@@ -391,7 +396,7 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     const int pos = decode_append_at(a, b);
     const T *knew = static_cast<const T *>(a.k_new) + ((int64_t)b * a.hkv + hk) * DFULL + d0;
     const T *vnew = static_cast<const T *>(a.v_new) + ((int64_t)b * a.hkv + hk) * DFULL + d0;
-    if (pos >= c0 && pos < c1 && lane < 2 * CH) {
+    if (pos >= c0 && pos < c1 && lane < 2 * CH && g_base == 0) {
         const T *src = (lane < CH ? knew : vnew) + cp_chunk * 8;
         T *dst = const_cast<T *>(lane < CH ? kbase + (int64_t)pos * a.k.st : vbase + (int64_t)pos * a.v.st) + cp_chunk * 8;
         *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
@@ -516,7 +521,7 @@ __global__ void __launch_bounds__(DM_WARPS * 32) decode_split_mma_kernel(DecodeA
     for (int rr = 0; rr < 2; ++rr) {
         l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
         l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
-        const int hg = g + 8 * rr;
+        const int hg = g_base + g + 8 * rr;
         if (hg < group) {
             const int h = hk * group + hg;
             const float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
@@ -676,7 +681,7 @@ static cudaError_t split_mma(const DecodeArgs &a, cudaStream_t stream) {
     constexpr size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_KEYS * 2 * D + (PARTS == 2 ? (size_t)DM_WARPS * 32 * 8 * sizeof(float) : 0);
     cudaError_t e = cudaFuncSetAttribute(decode_split_mma_kernel<T, D, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    const long long units = (long long)a.splits * a.hkv * PARTS;
+    const long long units = (long long)a.splits * a.hkv * PARTS * ((a.hq / a.hkv + 15) / 16);
     dim3 grid((unsigned)((units + DM_WARPS - 1) / DM_WARPS), a.b);
     decode_split_mma_kernel<T, D, PARTS><<<grid, DM_WARPS * 32, smem, stream>>>(a);
     return cudaGetLastError();
@@ -694,7 +699,7 @@ static bool decode_force_scalar_pass() {
 template <typename T>
 static cudaError_t decode_t(const DecodeArgs &a, bool vector_ok, cudaStream_t stream, int *launches) {
     cudaError_t e;
-    const bool mma = vector_ok && sizeof(T) == 2 && a.hq / a.hkv >= 4 && a.hq / a.hkv <= 16 && !decode_force_scalar_pass();
+    const bool mma = vector_ok && sizeof(T) == 2 && a.hq / a.hkv >= 3 && !decode_force_scalar_pass();
     if (mma && a.d == 128) e = split_mma<T, 128>(a, stream);
     else if (mma && a.d == 64) e = split_mma<T, 64>(a, stream);
     else if (mma && a.d == 256) e = split_mma<T, 256>(a, stream);

@@ -25,6 +25,8 @@ CASES = [
     ("tensor-core pass: D64, group 8", [3, 16, 2, 700, 64], [699, 0, 350], None),
     ("tensor-core pass: D64, window", [2, 8, 2, 1300, 64], [1299, 40], 100),
     ("tensor-core pass: D256 over warp pairs", [3, 8, 2, 900, 256], [899, 0, 450], None),
+    ("tensor-core pass: group of 32", [2, 32, 1, 800, 128], [799, 400], None),
+    ("tensor-core pass: group of 3", [2, 6, 2, 500, 128], [499, 7], 64),
     ("FMA pass: group 2, D128", [2, 4, 2, 520, 128], [519, 77], 64),
     ("scalar pass: odd head dimension", [2, 4, 2, 90, 40], [89, 30], 10),
 ]

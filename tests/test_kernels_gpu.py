@@ -227,6 +227,10 @@ def decode_cases():
         # and at 256, a row's features over two warps
         ("group of 16, D256, window", [2, 32, 2, 1100, 256], [1100, 600], 500),
         ("group of 4, D256, long", [2, 4, 1, 5000, 256], [4999, 17], None),
+        # groups of more than sixteen heads: several units of sixteen side by side (one key-value head: MQA)
+        ("group of 32, one kv head", [2, 32, 1, 1500, 128], [1500, 333], None),
+        ("group of 20, D64, window", [3, 40, 2, 700, 64], [700, 1, 350], 300),
+        ("group of 40, D256", [1, 40, 1, 600, 256], [577], None),
     ]
 
 
