@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
         if (a.has_p) t_keep = max(t_keep, radix_threshold<T, true>(z, a, bits, tid, TS, m, t_keep, radix));
 
         // 4. argmax of s + g over the kept tokens, ties to the lowest id; the kept tokens' mass.
-        float best = -INFINITY, wp = 0.f;
+        float best = -INFINITY, wp = 0.f, reach = -3.2f;
         int best_i = a.v;
         // g lies within [-3.13, 22.9] (the words' range), and the row's largest logit is always kept
         // (s = 0), so a token more than 26.1 below it is never drawn: it adds to the mass and skips
@@ -320,8 +320,19 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
             for (int e = 0; e < 4; ++e) {
                 const int i = 4 * g + e;
                 if (!(s4[e] >= -26.1f)) continue;
+                // g rises with the word, so most tokens are out of the running by their word alone: the winner
+                // scores at least `reach` (this thread's best so far; the row's largest logit alone reaches -3.13),
+                // and g < c exactly when u < exp(-exp(-c)).  With c = reach - s - 0.001 > 0 and a thousandth off
+                // the threshold, the two fast exponentials (relative error under 1e-5 here) can only let a token
+                // through that the exact variate then weighs, never turn one away that could win or tie.
+                const float c = reach - s4[e] - 1e-3f;
+                if (c > 0.f) {
+                    const float u = (static_cast<float>(w[e]) + 0.5f) * 2.3283064365386963e-10f;
+                    if (u < __expf(-__expf(-c)) * 0.999f) continue;
+                }
                 const float score = __fadd_rn(s4[e], gumbel_of_word(w[e]));
                 if (score > best || (score == best && i < best_i) || best_i == a.v) { best = score; best_i = i; }
+                reach = fmaxf(reach, best);
             }
         }
         // (score, id) pairs: the larger score, then the lower id.
