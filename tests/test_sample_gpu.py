@@ -134,3 +134,26 @@ def test_draws_follow_the_kept_distribution(name, options, kept):
     bound = df * (1 - 2 / (9 * df) + 3.719016 * np.sqrt(2 / (9 * df))) ** 3 if df > 0 else 1e-9   # Wilson-Hilferty at 1 - 1e-4
     assert chi2 <= bound, f"{name}: chi-square {chi2:.1f} over {df} degrees of freedom (bound {bound:.1f})"
     assert np.max(np.abs(sp - np.log(prob[[kept.index(t) for t in tokens]]))) <= 2e-6
+
+
+@pytest.mark.parametrize("dims", [(1, 1), (3, 2), (1, 151936), (200, 700)], ids=lambda d: f"{d[0]}x{d[1]}")
+def test_smallest_and_widest_calls(dims):
+    """One token, two tokens, one row over a cluster of eight blocks, more rows than multiprocessors."""
+    z = logits_of(*dims, "bf16", 55)
+    for options in (SampleOptions(seed=4), SampleOptions(temperature=0.8, top_k=2, top_p=0.7, seed=4), SampleOptions.greedy()):
+        got, want = run(z, "bf16", options), oracle_of(z, options)
+        assert np.array_equal(got[0], want[0])
+        for k in (1, 2, 3):
+            assert close(got[k], want[k])
+
+
+def test_rows_of_a_wider_buffer():
+    """The rows' stride is the caller's: logits that are a slice of a wider tensor are read in place."""
+    wide = logits_of(5, 3000, "f16", 56)
+    z = np.ascontiguousarray(wide[:, :2048])
+    t = torch.from_numpy(wide).to(DEV).to(torch.float16)[:, :2048]
+    assert t.stride(0) == 3000
+    options = SampleOptions(temperature=0.9, top_p=0.95, seed=11, offset=3)
+    out = sample(t, options)
+    want = oracle_of(z, options)
+    assert np.array_equal(out.tokens.cpu().numpy(), want[0]) and close(out.sampling_logprob.cpu().numpy(), want[3])
