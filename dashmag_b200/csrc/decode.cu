@@ -628,6 +628,51 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeArgs a) {
     __syncthreads();
     mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
 
+    if (a.d % 4 == 0) {
+        // Four head dimensions a thread (16-byte loads of the partials), the splits dealt over the
+        // 128 / (d / 4) groups of threads, whose sums meet in shared memory in group order.
+        __shared__ float4 part[128];
+        __shared__ float dens[128];
+        const int ct = a.d / 4, groups = 128 / ct;
+        const int c4 = threadIdx.x % ct, sg = threadIdx.x / ct;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        float den = 0.f;
+        for (int i0 = 0; i0 < n; i0 += MERGE_MAX) {
+            const int m = min(MERGE_MAX, n - i0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < m; i += blockDim.x) w[i] = expf(lse[i0 + i] - mx);
+            __syncthreads();
+            if (sg < groups) {
+#pragma unroll 4
+                for (int i = sg; i < m; i += groups) {
+                    const float wi = w[i];
+                    const float4 x = *reinterpret_cast<const float4 *>(po + (int64_t)(i0 + i) * a.d + 4 * c4);
+                    den += wi;
+                    num.x = fmaf(wi, x.x, num.x);
+                    num.y = fmaf(wi, x.y, num.y);
+                    num.z = fmaf(wi, x.z, num.z);
+                    num.w = fmaf(wi, x.w, num.w);
+                }
+            }
+        }
+        part[threadIdx.x] = num;
+        dens[threadIdx.x] = den;
+        __syncthreads();
+        if (sg == 0) {
+            for (int g = 1; g < groups; ++g) {
+                const float4 x = part[g * ct + c4];
+                num.x += x.x; num.y += x.y; num.z += x.z; num.w += x.w;
+                den += dens[g * ct + c4];
+            }
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            T *o = out + 4 * c4;
+            o[0] = Num<T>::from_f32(num.x * inv);
+            o[1] = Num<T>::from_f32(num.y * inv);
+            o[2] = Num<T>::from_f32(num.z * inv);
+            o[3] = Num<T>::from_f32(num.w * inv);
+        }
+        return;
+    }
     float num[2] = {0.f, 0.f}, den = 0.f;  // a.d <= 256: two head dimensions per thread at most
     for (int i0 = 0; i0 < n; i0 += MERGE_MAX) {
         const int m = min(MERGE_MAX, n - i0);
