@@ -581,6 +581,7 @@ int dash_sample(const dash_sample_params *p, const void *logits, void *tokens, f
     if ((rc = check_workspace(op, workspace, workspace_bytes, dash_sample_workspace(p))) != DASH_ATTN_OK) return rc;
     dash::SampleArgs a{};
     a.logits = logits; a.b = p->b; a.v = p->v; a.stride = p->row_stride;
+    a.vec = reinterpret_cast<uintptr_t>(logits) % 16 == 0 && (p->b == 1 || (p->row_stride * (int64_t)elem_bytes(p->dtype)) % 16 == 0);
     a.greedy = p->temperature == 0.f;
     a.tau = a.greedy ? 1.f : std::min(1.0f / p->temperature, 3.4028234663852886e38f);   // Cuts::inverse_temperature (:89-91)
     const size_t unmasked = (size_t)p->v - masked.size();

@@ -127,6 +127,25 @@ __device__ __forceinline__ float gumbel_of_word(uint32_t x) {
     return -logf(e);
 }
 
+// Every token of the row once, thread by thread: 16 bytes of logits a load where the rows allow it
+// (eight 16-bit logits or four f32 to a thread at a time), one logit a load otherwise.
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_logit(const T *z, int v, int tid, int TS, bool vec, F f) {
+    constexpr int E = 16 / sizeof(T);
+    int done = 0;
+    if (vec) {
+        const int nv = v / E;
+        for (int j = tid; j < nv; j += TS) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(z + (size_t)j * E);
+            const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+            for (int k = 0; k < E; ++k) f(j * E + k, e[k]);
+        }
+        done = nv * E;
+    }
+    for (int i = done + tid; i < v; i += TS) f(i, z[i]);
+}
+
 // Shared memory of the threshold search: a histogram of 256 bins per warp (counts, and tempered
 // masses in fixed point: integer sums do not depend on the order the atomics land in, so the search
 // gives the same threshold on every run), and the block's totals, which the cluster's other blocks read.
@@ -163,16 +182,21 @@ __device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint3
             if (MASS) (&sm.mass[0][0][0])[i] = 0;
         }
         __syncthreads();
-        for (int i = tid; i < a.v; i += TS) {
+        for_each_logit(z, a.v, tid, TS, a.vec != 0, [&](int i, T zi) {
             const bool gone = bits != nullptr && ((bits[i >> 5] >> (i & 31)) & 1u) != 0;
-            if (MASS && gone) continue;
-            const uint32_t key = gone ? key_ninf : Key<T>::of(z[i]);
-            if (key < floor_key) continue;
-            if (level > 0 && (key >> (shift + 8)) != prefix) continue;
+            if (MASS && gone) return;
+            const uint32_t key = gone ? key_ninf : Key<T>::of(zi);
+            if (key < floor_key) return;
+            if (level > 0 && (key >> (shift + 8)) != prefix) return;
             const uint32_t d = (key >> shift) & 255u;
+            if (MASS) {
+                // Weights under 2^-41 round to nothing and are left out (the largest logit's is 1).
+                const unsigned long long w = __float2ull_rn(expf(__fmul_rn(Num<T>::to_f32(zi) - m, a.tau)) * MASS_ONE);
+                if (w == 0) return;
+                atomicAdd(&sm.mass[warp >> 2][d][lane & 3], w);
+            }
             atomicAdd(&sm.cnt[warp >> 2][d][lane & 3], 1u);
-            if (MASS) atomicAdd(&sm.mass[warp >> 2][d][lane & 3], __float2ull_rn(expf(__fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau)) * MASS_ONE));
-        }
+        });
         __syncthreads();
         if (threadIdx.x < 256) {
             uint32_t c = 0;
@@ -265,20 +289,21 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
 
     // 1. m = max over the unmasked tokens; 2. sum exp(z - m) (and, tempered, sum exp((z - m) tau)).
     float m = -INFINITY;
-    for (int i = tid; i < a.v; i += TS)
-        if (!masked(i)) m = fmaxf(m, Num<T>::to_f32(z[i]));
+    for_each_logit(z, a.v, tid, TS, a.vec != 0, [&](int i, T zi) {
+        if (!masked(i)) m = fmaxf(m, Num<T>::to_f32(zi));
+    });
     m = row_reduce(m, MaxOp(), fs, &fslot);
     const bool degenerate = m == -INFINITY;   // no finite unmasked logit: the lowest unmasked id, NaN
     const bool tempered_differs = !a.greedy && a.tau != 1.0f;
     float s1 = 0.f, wu = 0.f;
     int first = a.v;   // the lowest unmasked id holding the maximum
-    for (int i = tid; i < a.v; i += TS) {
-        if (masked(i)) continue;
-        const float x = Num<T>::to_f32(z[i]);
+    for_each_logit(z, a.v, tid, TS, a.vec != 0, [&](int i, T zi) {
+        if (masked(i)) return;
+        const float x = Num<T>::to_f32(zi);
         s1 += expf(x - m);
         if (tempered_differs) wu += expf((x - m) * a.tau);
         if (x == m && i < first) first = i;
-    }
+    });
     s1 = row_reduce(s1, AddOp(), fs, &fslot);
     if (tempered_differs) wu = row_reduce(wu, AddOp(), fs, &fslot);
     const float lse = m + logf(s1);
@@ -301,19 +326,20 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
         // g lies within [-3.13, 22.9] (the words' range), and the row's largest logit is always kept
         // (s = 0), so a token more than 26.1 below it is never drawn: it adds to the mass and skips
         // the generator and the logarithms.
-        for (int g = tid; g < (a.v + 3) / 4; g += TS) {
+        // Four tokens (one Philox call) at a time: `zs` their logits, read by the caller.
+        auto draw4 = [&](int g, const T (&zs)[4]) {
             float s4[4];
             bool draw = false;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = 4 * g + e;
                 s4[e] = -INFINITY;
-                if (i >= a.v || masked(i) || Key<T>::of(z[i]) < t_keep) continue;
-                s4[e] = __fmul_rn(Num<T>::to_f32(z[i]) - m, a.tau);
+                if (i >= a.v || masked(i) || Key<T>::of(zs[e]) < t_keep) continue;
+                s4[e] = __fmul_rn(Num<T>::to_f32(zs[e]) - m, a.tau);
                 if (cut) wp += expf(s4[e]);
                 draw = draw || s4[e] >= -26.1f;
             }
-            if (!draw) continue;
+            if (!draw) return;
             uint32_t w[4];
             philox4x32_10((uint32_t)g, (uint32_t)row, a.off_lo, a.off_hi, a.key0, a.key1, w);
 #pragma unroll
@@ -334,6 +360,27 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
                 if (score > best || (score == best && i < best_i) || best_i == a.v) { best = score; best_i = i; }
                 reach = fmaxf(reach, best);
             }
+        };
+        constexpr int E = 16 / sizeof(T);   // logits to a 16-byte load: one or two groups of four
+        int g0 = 0;
+        if (a.vec) {
+            const int nv = a.v / E;
+            for (int j = tid; j < nv; j += TS) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(z + (size_t)j * E);
+                const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+                for (int sub = 0; sub < E / 4; ++sub) {
+                    const T zs[4] = {e[4 * sub], e[4 * sub + 1], e[4 * sub + 2], e[4 * sub + 3]};
+                    draw4(j * (E / 4) + sub, zs);
+                }
+            }
+            g0 = nv * (E / 4);
+        }
+        for (int g = g0 + tid; g < (a.v + 3) / 4; g += TS) {
+            T zs[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) zs[e] = 4 * g + e < a.v ? z[4 * g + e] : z[0];
+            draw4(g, zs);
         }
         // (score, id) pairs: the larger score, then the lower id.
         {

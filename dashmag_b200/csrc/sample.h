@@ -9,6 +9,7 @@ struct SampleArgs {
     const void *logits;      // [B, V], rows `stride` elements apart, the vocabulary contiguous
     int b, v;
     int64_t stride;
+    int vec;                 // every row starts on a 16-byte boundary
     int greedy;              // temperature 0
     float tau;               // 1 / temperature as f32, at most f32::MAX
     int top_k;               // 0: top-k cuts nothing (k = 0 or k >= the unmasked tokens)
