@@ -543,6 +543,8 @@ static int check_sample(const dash_sample_params *p, std::vector<uint32_t> *mask
         return fail(DASH_ATTN_INVALID, "%s: logits must be f32, bf16 or f16, got code %d", op, p->dtype);
     if (p->b < 0 || p->v < 0) return fail(DASH_ATTN_INVALID, "%s: logits must be [B, V], got [%d, %d]", op, p->b, p->v);
     if (p->v == 0) return fail(DASH_ATTN_INVALID, "%s: the vocabulary is empty", op);
+    // The top-p search sums 14-bit pieces of the weights in 32-bit words, a thirty-second of a row to a word.
+    if (p->v > (1 << 22)) return fail(DASH_ATTN_UNSUPPORTED, "%s: a vocabulary of %d tokens; up to 4194304 are taken", op, p->v);
     if (!(std::isfinite(p->temperature) && p->temperature >= 0.f))
         return fail(DASH_ATTN_INVALID, "%s: the temperature must be finite and >= 0, got %g", op, (double)p->temperature);
     if (!(p->top_p >= 0.f && p->top_p <= 1.f))

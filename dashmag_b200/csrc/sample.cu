@@ -153,7 +153,9 @@ struct RadixSmem {
     // 32 copies of each bin: copy c of bin d at [c / 4][d][c % 4]; a thread uses copy 4 (warp / 4) + lane % 4, so
     // that the lanes of a warp that meet in one bin (16-bit logits crowd into a few top bytes) spread over four words.
     uint32_t cnt[8][256][4];
-    unsigned long long mass[8][256][4];
+    // A mass (41 bits of fixed point) as three pieces of 14, 14 and 13 bits in three 32-bit words: 32-bit
+    // shared-memory atomics are native, 64-bit ones are not, and a copy's few thousand tokens cannot overflow a piece.
+    uint32_t mass[3][8][256][4];
     uint32_t tcnt[256];
     unsigned long long tmass[256];
     uint32_t sel, above_cnt;
@@ -179,7 +181,7 @@ __device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint3
         const int shift = Key<T>::BITS - 8 * (level + 1);
         for (int i = threadIdx.x; i < 32 * 256; i += ST) {
             (&sm.cnt[0][0][0])[i] = 0;
-            if (MASS) (&sm.mass[0][0][0])[i] = 0;
+            if (MASS) { (&sm.mass[0][0][0][0])[i] = 0; (&sm.mass[1][0][0][0])[i] = 0; (&sm.mass[2][0][0][0])[i] = 0; }
         }
         __syncthreads();
         for_each_logit(z, a.v, tid, TS, a.vec != 0, [&](int i, T zi) {
@@ -193,7 +195,9 @@ __device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint3
                 // Weights under 2^-41 round to nothing and are left out (the largest logit's is 1).
                 const unsigned long long w = __float2ull_rn(expf(__fmul_rn(Num<T>::to_f32(zi) - m, a.tau)) * MASS_ONE);
                 if (w == 0) return;
-                atomicAdd(&sm.mass[warp >> 2][d][lane & 3], w);
+                atomicAdd(&sm.mass[0][warp >> 2][d][lane & 3], (uint32_t)(w & 0x3fffu));
+                if (w >> 14) atomicAdd(&sm.mass[1][warp >> 2][d][lane & 3], (uint32_t)((w >> 14) & 0x3fffu));
+                if (w >> 28) atomicAdd(&sm.mass[2][warp >> 2][d][lane & 3], (uint32_t)(w >> 28));
             }
             atomicAdd(&sm.cnt[warp >> 2][d][lane & 3], 1u);
         });
@@ -203,7 +207,8 @@ __device__ uint32_t radix_threshold(const T *z, const SampleArgs &a, const uint3
             unsigned long long w = 0;
             for (int x = 0; x < 32; ++x) {
                 c += sm.cnt[x >> 2][threadIdx.x][x & 3];
-                if (MASS) w += sm.mass[x >> 2][threadIdx.x][x & 3];
+                if (MASS) w += (unsigned long long)sm.mass[0][x >> 2][threadIdx.x][x & 3] + ((unsigned long long)sm.mass[1][x >> 2][threadIdx.x][x & 3] << 14) +
+                               ((unsigned long long)sm.mass[2][x >> 2][threadIdx.x][x & 3] << 28);
             }
             sm.tcnt[threadIdx.x] = c;
             sm.tmass[threadIdx.x] = w;
