@@ -157,3 +157,45 @@ def test_rows_of_a_wider_buffer():
     out = sample(t, options)
     want = oracle_of(z, options)
     assert np.array_equal(out.tokens.cpu().numpy(), want[0]) and close(out.sampling_logprob.cpu().numpy(), want[3])
+
+
+def random_calls(count, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        v = int(rng.choice([7, 64, 257, 1000, 4099, 20000]))
+        b = int(rng.integers(1, 6))
+        dtype = str(rng.choice(["f32", "bf16", "f16"]))
+        masked = tuple(int(x) for x in rng.choice(v, size=int(rng.integers(0, min(v - 1, 6))), replace=False))
+        options = SampleOptions(temperature=float(rng.choice([0.0, 0.3, 0.7, 1.0, 1.5, 4.0])), top_k=int(rng.choice([0, 1, 2, 5, 40, v, v + 3])),
+                                top_p=float(rng.choice([1.0, 0.99, 0.9, 0.5, 0.1, 0.0])), seed=int(rng.integers(0, 2 ** 62)),
+                                offset=int(rng.integers(0, 2 ** 40)), masked=masked)
+        scale = float(rng.choice([0.5, 3.0, 10.0]))
+        ties = bool(rng.random() < 0.3)
+        out.append((f"call {i}: {b}x{v} {dtype} T{options.temperature} k{options.top_k} p{options.top_p} m{len(masked)} scale{scale}{' ties' if ties else ''}",
+                    b, v, dtype, options, scale, ties, 5000 + i))
+    return out
+
+
+CALLS = random_calls(60, 20261125)
+
+
+@pytest.mark.parametrize("name,b,v,dtype,options,scale,ties,seed", CALLS, ids=[c[0] for c in CALLS])
+def test_random_calls(name, b, v, dtype, options, scale, ties, seed):
+    """A seeded sweep over sizes, dtypes, options and masked ids nobody chose; rows of few distinct values put
+    whole groups of ties at the cuts."""
+    z = logits_of(b, v, dtype, seed, scale)
+    if ties:
+        z = round_to(np.round(z * 2) / 2, dtype)
+    if v > 10 and seed % 3 == 0:
+        z[0, 3:9] = -np.inf   # tokens the model rules out
+    got, want = run(z, dtype, options), oracle_of(z, options)
+    for r in np.nonzero(got[0] != want[0])[0]:
+        tau = float(S.inverse_temperature(options.temperature)) if options.temperature > 0 else 1.0
+        g = S.gumbel_of_inputs(S.row_inputs(options.seed, options.offset, int(r), v))
+        with np.errstate(invalid="ignore"):
+            score = (z[r] - np.max(np.delete(z[r], list(options.masked)))) * tau + g
+        assert options.temperature > 0 and abs(score[got[0][r]] - score[want[0][r]]) <= 4e-6 * max(1.0, abs(score[want[0][r]])), f"row {r}: {got[0][r]} vs {want[0][r]}"
+    same = got[0] == want[0]
+    for k in (1, 2, 3):
+        assert close(got[k][same], want[k][same]), f"output {k}: {got[k]} vs {want[k]}"
