@@ -1,4 +1,4 @@
-"""A seeded sweep of shapes over the tensor-core kernels (bf16, D = 128 and D = 64): sizes and masks drawn at
+"""A seeded sweep of shapes over the tensor-core kernels (bf16, D = 128 and D = 64, and the D = 256 forward): sizes and masks drawn at
 random so that tile boundaries, sequence boundaries, windows and padding fall in places nobody
 chose, every case against the f64 oracle and run twice for identical bits (the pipelines hand
 tiles between warps through barriers; a lost ordering shows as a run-to-run difference)."""
@@ -57,7 +57,7 @@ def random_cases(count, seed, d=128):
     return out
 
 
-CASES = random_cases(40, 20261125) + random_cases(20, 20261126, d=64)
+CASES = random_cases(40, 20261125) + random_cases(20, 20261126, d=64) + random_cases(12, 20261127, d=256)
 # o, lse, dq, dk, dv relative to each result's largest value.  The gradients are sums of products of
 # values rounded to bf16 (P, dS: 2^-9 each), so their error grows with the number of terms and the
 # bounds of the fixed shapes (test_kernels_gpu.OWN) are a quarter too tight for shapes drawn at
