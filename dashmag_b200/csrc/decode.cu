@@ -291,9 +291,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(DecodeArgs
 }
 
 // ---------------------------------------------------------------------------------------------
-// The split pass on the tensor cores (16-bit cache, head dimension 64, 128 or 256, groups of up to 16 heads)
+// The split pass on the tensor cores (16-bit cache, head dimension 64, 128 or 256, groups of two heads or more)
 // ---------------------------------------------------------------------------------------------
-// With four or more query heads to a key-value head the scalar pass spends its time on FMA issue,
+// With several query heads to a key-value head the scalar pass spends its time on FMA issue,
 // not on HBM: a cache row of 512 bytes feeds 2048 multiply-adds.  Here the query heads of the group
 // are the M dimension of warp-level MMAs (m16n8k16): S = Q K^T with the 16 keys of a tile as two
 // N tiles, then O += P V with P taken straight from the accumulator registers of S as the A
@@ -744,7 +744,7 @@ static bool decode_force_scalar_pass() {
 template <typename T>
 static cudaError_t decode_t(const DecodeArgs &a, bool vector_ok, cudaStream_t stream, int *launches) {
     cudaError_t e;
-    const bool mma = vector_ok && sizeof(T) == 2 && a.hq / a.hkv >= 3 && !decode_force_scalar_pass();
+    const bool mma = vector_ok && sizeof(T) == 2 && a.hq / a.hkv >= 2 && !decode_force_scalar_pass();
     if (mma && a.d == 128) e = split_mma<T, 128>(a, stream);
     else if (mma && a.d == 64) e = split_mma<T, 64>(a, stream);
     else if (mma && a.d == 256) e = split_mma<T, 256>(a, stream);
