@@ -328,9 +328,10 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
         // 4. argmax of s + g over the kept tokens, ties to the lowest id; the kept tokens' mass.
         float best = -INFINITY, wp = 0.f, reach = -3.2f;
         int best_i = a.v;
-        // g lies within [-3.13, 22.9] (the words' range), and the row's largest logit is always kept
-        // (s = 0), so a token more than 26.1 below it is never drawn: it adds to the mass and skips
-        // the generator and the logarithms.
+        // g lies within [-3.13, 22.9] (the words' range) and the winner scores at least `reach` (this thread's
+        // best so far; the row's largest logit, always kept, alone reaches -3.13), so a token with s < reach - 22.95
+        // is never drawn - at the start that is 26.1 below the largest logit, the contract's own bound: it adds to
+        // the mass and skips the generator and the logarithms.
         // Four tokens (one Philox call) at a time: `zs` their logits, read by the caller.
         auto draw4 = [&](int g, const T (&zs)[4]) {
             float s4[4];
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
                 if (i >= a.v || masked(i) || Key<T>::of(zs[e]) < t_keep) continue;
                 s4[e] = __fmul_rn(Num<T>::to_f32(zs[e]) - m, a.tau);
                 if (cut) wp += expf(s4[e]);
-                draw = draw || s4[e] >= -26.1f;
+                draw = draw || s4[e] >= reach - 22.95f;
             }
             if (!draw) return;
             uint32_t w[4];
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(ST) sample_kernel(SampleArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = 4 * g + e;
-                if (!(s4[e] >= -26.1f)) continue;
+                if (!(s4[e] >= reach - 22.95f)) continue;
                 // g rises with the word, so most tokens are out of the running by their word alone: the winner
                 // scores at least `reach` (this thread's best so far; the row's largest logit alone reaches -3.13),
                 // and g < c exactly when u < exp(-exp(-c)).  With c = reach - s - 0.001 > 0 and a thousandth off
