@@ -22,6 +22,7 @@ PROBES = {
     "atomic_runs": 3,
     "tensor_core_runs": 4,
     "generic_runs": 5,
+    "tensor_map_encodes": 6,
 }
 
 i32, i64, f32, vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p
@@ -131,6 +132,7 @@ PROTOTYPES = {
     "dash_attn_last_error": (ctypes.c_char_p, []),
     "dash_attn_probe": (ctypes.c_uint64, [ctypes.c_int]),
     "dash_attn_force_generic": (None, [ctypes.c_int]),
+    "dash_attn_force_tensor": (None, [ctypes.c_int]),
 }
 
 _lib = None

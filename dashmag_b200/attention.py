@@ -51,6 +51,12 @@ def _stream(device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def _on(device):
+    """Makes the tensors' device the current one for the call: the library launches on the current
+    device, and the caller's may be another (one process driving several GPUs)."""
+    return torch.cuda.device(device)
+
+
 def _strides(t: torch.Tensor, n: int):
     return (ctypes.c_int64 * n)(*t.stride())
 
@@ -150,8 +156,9 @@ def attention_with_lse(query, key, value, mask: AttentionMask = AttentionMask.no
     out = torch.empty((b, tq, hq, d), dtype=query.dtype, device=query.device)
     lse = torch.empty((b, tq, hq), dtype=torch.float32, device=query.device)
     ws = _workspace(lib.dash_attn_forward_workspace(ctypes.byref(p)), query.device)
-    rc = lib.dash_attn_forward(ctypes.byref(p), _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(lse),
-                               _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
+    with _on(query.device):
+        rc = lib.dash_attn_forward(ctypes.byref(p), _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(lse),
+                                   _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
     if rc != _lib.OK:
         _raise(rc)
     return out, lse
@@ -185,9 +192,10 @@ def attention_backward(query, key, value, output, lse, grad_output, mask: Attent
     dk = torch.empty(key.shape, dtype=key.dtype, device=query.device)
     dv = torch.empty(value.shape, dtype=value.dtype, device=query.device)
     ws = _workspace(lib.dash_attn_backward_workspace(ctypes.byref(p)), query.device)
-    rc = lib.dash_attn_backward(ctypes.byref(p), _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(lse),
-                                _ptr(grad_output), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ws),
-                                0 if ws is None else ws.numel(), _stream(query.device))
+    with _on(query.device):
+        rc = lib.dash_attn_backward(ctypes.byref(p), _ptr(query), _ptr(key), _ptr(value), _ptr(output), _ptr(lse),
+                                    _ptr(grad_output), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ws),
+                                    0 if ws is None else ws.numel(), _stream(query.device))
     if rc != _lib.OK:
         _raise(rc)
     return dq, dk, dv
@@ -239,8 +247,9 @@ def attention_decode(query, key, value, cache_lengths=None, options: AttentionOp
     lib = _lib.lib()
     out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
     ws = _workspace(lib.dash_attn_decode_workspace(ctypes.byref(p)), query.device)
-    rc = lib.dash_attn_decode(ctypes.byref(p), _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(ws),
-                              0 if ws is None else ws.numel(), _stream(query.device))
+    with _on(query.device):
+        rc = lib.dash_attn_decode(ctypes.byref(p), _ptr(query), _ptr(key), _ptr(value), _ptr(out), _ptr(ws),
+                                  0 if ws is None else ws.numel(), _stream(query.device))
     if rc != _lib.OK:
         _raise(rc)
     return out
@@ -266,8 +275,9 @@ def attention_decode_append(query, new_key, new_value, key, value, cache_lengths
     lib = _lib.lib()
     out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
     ws = _workspace(lib.dash_attn_decode_workspace(ctypes.byref(p)), query.device)
-    rc = lib.dash_attn_decode_append(ctypes.byref(p), _ptr(query), _ptr(new_key), _ptr(new_value), _ptr(key), _ptr(value),
-                                     _ptr(out), _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
+    with _on(query.device):
+        rc = lib.dash_attn_decode_append(ctypes.byref(p), _ptr(query), _ptr(new_key), _ptr(new_value), _ptr(key), _ptr(value),
+                                         _ptr(out), _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
     if rc != _lib.OK:
         _raise(rc)
     return out

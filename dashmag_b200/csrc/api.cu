@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <initializer_list>
 #include <algorithm>
 #include <string>
 #include <vector>
@@ -23,6 +24,7 @@ namespace {
 thread_local std::string g_error;
 std::atomic<uint64_t> g_probe[DASH_ATTN_PROBE_COUNT];
 std::atomic<int> g_force_generic{0};
+std::atomic<int> g_force_tensor{0};
 
 int fail(int code, const char *fmt, ...) {
     char buf[512];
@@ -150,7 +152,15 @@ int check_workspace(const char *op, void *ws, size_t have, size_t need) {
 
 int train_path(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
     if (g_force_generic.load()) return 0;
-    return dash::sm100_takes(p, q, k, v, backward) ? 1 : 0;
+    return dash::sm100_takes(p, q, k, v, backward, g_force_tensor.load() != 0) ? 1 : 0;
+}
+
+// The tensor-core kernels write their outputs (and read dO) through TMA tiles and 16-byte vectors:
+// a call whose output is not 16-byte aligned goes to the generic kernels, like one whose input is not.
+bool aligned16(std::initializer_list<const void *> ptrs) {
+    for (const void *x : ptrs)
+        if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return false;
+    return true;
 }
 
 // ---- decode ---------------------------------------------------------------------------------
@@ -184,9 +194,14 @@ int check_decode(const dash_attn_decode_params *p, const char *op = "attention_d
 // the partial outputs stay a few percent of the cache traffic.  A pure function of the shape, so
 // the workspace query and the launch agree without looking at the device.
 void decode_plan(const dash_attn_decode_params *p, int *chunk, int *splits) {
+    // DASH_ATTN_DECODE_CHUNK (read once, when the first plan is made) fixes the chunk for comparison runs.
+    static const long long fixed = [] {
+        const char *env = std::getenv("DASH_ATTN_DECODE_CHUNK");
+        return env ? std::atoll(env) : 0LL;
+    }();
     long long c = 512;
-    if (const char *env = std::getenv("DASH_ATTN_DECODE_CHUNK")) {
-        c = std::atoll(env);
+    if (fixed > 0) {
+        c = fixed;
     } else {
         // Chunks of 128 to 512 keys, as long as they still leave units (a chunk of a key-value head;
         // a group of more than sixteen query heads counts once per sixteen) to fill the warps of the GPU:
@@ -224,10 +239,12 @@ const char *dash_attn_last_error(void) { return g_error.c_str(); }
 
 uint64_t dash_attn_probe(int which) {
     if (which < 0 || which >= DASH_ATTN_PROBE_COUNT) return 0;
+    if (which == DASH_ATTN_PROBE_TENSOR_MAP_ENCODES) return dash::sm100_tensor_map_encodes();
     return g_probe[which].load();
 }
 
 void dash_attn_force_generic(int on) { g_force_generic.store(on ? 1 : 0); }
+void dash_attn_force_tensor(int on) { g_force_tensor.store(on ? 1 : 0); }
 
 int dash_attn_device_status(int clear) {
     g_error.clear();
@@ -299,7 +316,7 @@ int dash_attn_forward(const dash_attn_params *p, const void *q, const void *k, c
     a.out = o;
     a.lse = lse;
     cudaError_t e;
-    if (train_path(p, q, k, v, 0) == 1) {
+    if (train_path(p, q, k, v, 0) == 1 && aligned16({o})) {
         e = dash::sm100_forward(p, a, workspace, stream, &launches, g_error);
         if (e == cudaSuccess && !g_error.empty()) return DASH_ATTN_CUDA;
         g_probe[DASH_ATTN_PROBE_TENSOR_CORE_RUNS] += 1;
@@ -344,7 +361,7 @@ int dash_attn_backward(const dash_attn_params *p, const void *q, const void *k, 
     a.dq = dq; a.dk = dk; a.dv = dv;
     void *extra = static_cast<char *>(workspace) + align256(sizeof(float) * (size_t)p->b * p->tq * p->hq);
     cudaError_t e;
-    if (train_path(p, q, k, v, 1) == 1 && reinterpret_cast<uintptr_t>(dout) % 16 == 0) {
+    if (train_path(p, q, k, v, 1) == 1 && aligned16({dout, dq, dk, dv})) {
         bool atomic = false;
         e = dash::sm100_backward(p, a, extra, stream, &launches, &atomic, g_error);
         if (e == cudaSuccess && !g_error.empty()) return DASH_ATTN_CUDA;
@@ -361,9 +378,11 @@ int dash_attn_backward(const dash_attn_params *p, const void *q, const void *k, 
 }
 
 // The decoding step, with (k_new, v_new set) or without the new row written into the cache first.
+// The split pass's partial outputs go to the caller's workspace, or (`library_array`) to the array the
+// library itself holds on the device.
 static int decode_impl(const char *op, const dash_attn_decode_params *p, const void *q, const void *k_new, const void *v_new,
                        const void *k_cache, const void *v_cache, void *out, void *workspace, size_t workspace_bytes,
-                       dash_attn_stream_t stream_) {
+                       dash_attn_stream_t stream_, bool library_array = false) {
     g_error.clear();
     int rc = check_decode(p, op);
     if (rc != DASH_ATTN_OK) return rc;
@@ -377,10 +396,33 @@ static int decode_impl(const char *op, const dash_attn_decode_params *p, const v
         return e == cudaSuccess ? DASH_ATTN_OK : cuda_fail(op, e);
     }
     if (!q || !k_cache || !v_cache) return fail(DASH_ATTN_INVALID, "%s: a tensor pointer is null", op);
-    size_t need = dash_attn_decode_workspace(p);
-    if ((rc = check_workspace(op, workspace, workspace_bytes, need)) != DASH_ATTN_OK) return rc;
 
     dash::DecodeArgs a{};
+    decode_plan(p, &a.chunk, &a.splits);
+    if (library_array) {
+        // Fewer, longer splits until the partials fit the library's array.
+        const size_t capacity = dash::decode_static_capacity_floats();
+        const size_t per_split = (size_t)p->b * p->hq * ((size_t)p->d + 1) + 64;
+        if (per_split > capacity)
+            return fail(DASH_ATTN_UNSUPPORTED,
+                        "%s: B * Hq * (D + 1) = %zu floats of partial output exceed the library's %zu-float (16 MiB) "
+                        "scratch; use dash_attn_decode with a workspace", op, per_split - 64, capacity);
+        while ((size_t)a.splits * per_split > capacity) {
+            a.chunk *= 2;
+            a.splits = (p->s + a.chunk - 1) / a.chunk;
+        }
+        float *scratch = nullptr;
+        cudaError_t e = dash::decode_static_scratch(&scratch);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+        a.part_o = scratch;
+        a.part_lse = scratch + (((size_t)p->b * p->hq * a.splits * p->d + 63) & ~size_t(63));
+    } else {
+        size_t need = dash_attn_decode_workspace(p);
+        if ((rc = check_workspace(op, workspace, workspace_bytes, need)) != DASH_ATTN_OK) return rc;
+        a.part_o = static_cast<float *>(workspace);
+        a.part_lse = reinterpret_cast<float *>(static_cast<char *>(workspace) +
+                                               align256(sizeof(float) * (size_t)p->b * p->hq * a.splits * p->d));
+    }
     a.b = p->b; a.s = p->s; a.hq = p->hq; a.hkv = p->hkv; a.d = p->d;
     a.scale = scale_for(p->has_scale, p->scale, p->d);
     a.q = q;
@@ -394,10 +436,6 @@ static int decode_impl(const char *op, const dash_attn_decode_params *p, const v
     // The window's left side binds only within S + 1 positions (reference.rs:445).
     int64_t none = (int64_t)p->s + 1;
     a.left = (int)((p->has_window && p->window_left >= 0 && p->window_left < none) ? p->window_left : none);
-    decode_plan(p, &a.chunk, &a.splits);
-    a.part_o = static_cast<float *>(workspace);
-    a.part_lse = reinterpret_cast<float *>(static_cast<char *>(workspace) +
-                                           align256(sizeof(float) * (size_t)p->b * p->hq * a.splits * p->d));
     a.out = out;
     bool vec = (p->d == 64 || p->d == 128 || p->d == 256) && vector_readable(q, p->q_stride, 3, eb) &&
                vector_readable(k_cache, p->k_stride, 4, eb) && vector_readable(v_cache, p->v_stride, 4, eb) &&
@@ -611,63 +649,8 @@ int dash_sample(const dash_sample_params *p, const void *logits, void *tokens, f
 
 int dash_attn_decode_static(const dash_attn_decode_params *p, const void *q, const void *k_cache,
                             const void *v_cache, void *out, dash_attn_stream_t stream_) {
-    const char *op = "attention_decode (static scratch)";
-    g_error.clear();
-    int rc = check_decode(p);
-    if (rc != DASH_ATTN_OK) return rc;
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    const size_t eb = elem_bytes(p->dtype);
-    size_t ob = (size_t)p->b * p->hq * p->d * eb;
-    if (ob == 0) return DASH_ATTN_OK;
-    if (!out) return fail(DASH_ATTN_INVALID, "%s: the output is null", op);
-    if (p->s == 0) {
-        cudaError_t e = cudaMemsetAsync(out, 0, ob, stream);
-        return e == cudaSuccess ? DASH_ATTN_OK : cuda_fail(op, e);
-    }
-    if (!q || !k_cache || !v_cache) return fail(DASH_ATTN_INVALID, "%s: a tensor pointer is null", op);
-
-    // Fewer, longer splits until the partials fit the library's array.
-    const size_t capacity = dash::decode_static_capacity_floats();
-    const size_t per_split = (size_t)p->b * p->hq * ((size_t)p->d + 1) + 64;
-    if (per_split > capacity)
-        return fail(DASH_ATTN_UNSUPPORTED,
-                    "%s: B * Hq * (D + 1) = %zu floats of partial output exceed the library's %zu-float (16 MiB) "
-                    "scratch; use dash_attn_decode with a workspace", op, per_split - 64, capacity);
-    int chunk, splits;
-    decode_plan(p, &chunk, &splits);
-    while ((size_t)splits * per_split > capacity) {
-        chunk *= 2;
-        splits = (p->s + chunk - 1) / chunk;
-    }
-    float *scratch = nullptr;
-    cudaError_t e = dash::decode_static_scratch(&scratch);
-    if (e != cudaSuccess) return cuda_fail(op, e);
-
-    dash::DecodeArgs a{};
-    a.b = p->b; a.s = p->s; a.hq = p->hq; a.hkv = p->hkv; a.d = p->d;
-    a.scale = scale_for(p->has_scale, p->scale, p->d);
-    a.q = q;
-    a.q_sb = p->q_stride[0]; a.q_sh = p->q_stride[1]; a.q_sd = p->q_stride[2];
-    a.k = view(k_cache, p->k_stride);
-    a.v = view(v_cache, p->v_stride);
-    a.lengths = p->lengths;
-    a.len_bytes = p->lengths_elem_bytes;
-    int64_t none = (int64_t)p->s + 1;
-    a.left = (int)((p->has_window && p->window_left >= 0 && p->window_left < none) ? p->window_left : none);
-    a.chunk = chunk;
-    a.splits = splits;
-    a.part_o = scratch;
-    size_t o_floats = ((size_t)p->b * p->hq * splits * p->d + 63) & ~size_t(63);
-    a.part_lse = scratch + o_floats;
-    a.out = out;
-    bool vec = (p->d == 64 || p->d == 128 || p->d == 256) && vector_readable(q, p->q_stride, 3, eb) &&
-               vector_readable(k_cache, p->k_stride, 4, eb) && vector_readable(v_cache, p->v_stride, 4, eb);
-    int launches = 0;
-    e = dash::launch_decode(p->dtype, a, vec, stream, &launches);
-    g_probe[DASH_ATTN_PROBE_KERNEL_LAUNCHES] += launches;
-    g_probe[DASH_ATTN_PROBE_GENERIC_RUNS] += 1;
-    if (e != cudaSuccess) return cuda_fail(op, e);
-    return DASH_ATTN_OK;
+    return decode_impl("attention_decode (static scratch)", p, q, nullptr, nullptr, k_cache, v_cache, out, nullptr, 0,
+                       stream_, true);
 }
 
 }  // extern "C"

@@ -46,7 +46,6 @@ constexpr int BIG_HALF = BIG * 128;        // 128 rows of 128 bytes: 64 columns 
 // A tile of head dimension HD (128 or 64) is HD / 64 such halves: 32 KiB at 128.
 template <int HD> constexpr int tile_bytes() { return (HD / 64) * BIG_HALF; }
 constexpr int QS = BIG;                    // rows of a streamed tile: a step
-constexpr int POLY_OF4 = 1;                // of every four exponentials, how many run on the FMA pipe (ex2_poly3)
 constexpr int KCG = 4;                     // elementwise warps per TMEM lane quadrant
 constexpr int KQW = QS / KCG;              // columns of a step per elementwise thread
 constexpr int KEW_THREADS = 32 * 4 * KCG;
@@ -73,6 +72,10 @@ template <> struct Pack<__half> {
         return *reinterpret_cast<uint32_t *>(&v);
     }
 };
+
+// Of every four exponentials, how many run on the FMA pipe (ex2_poly3): one for bf16, whose rounding step
+// (2^-9) is thirty times the cubic's error; none for f16, whose step (2^-12) is only four times it.
+template <typename T> constexpr int poly_of4() { return Pack<T>::FMT == 1 ? 1 : 0; }
 
 // `groups` x 32 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as
 // contiguous elements of the row.
@@ -518,10 +521,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 for (int c4 = 0; c4 < KQW / 8; ++c4) {
                     const int c = half * (KQW / 2) + c4 * 4;
                     const float4 l2 = *reinterpret_cast<const float4 *>(&aux.lse2[col0 + c]);
-                    p[c + 0] = exp2_mixed<(POLY_OF4 > 3)>(fmaf(p[c + 0], a.scale_log2, -l2.x));
-                    p[c + 1] = exp2_mixed<(POLY_OF4 > 1)>(fmaf(p[c + 1], a.scale_log2, -l2.y));
-                    p[c + 2] = exp2_mixed<(POLY_OF4 > 2)>(fmaf(p[c + 2], a.scale_log2, -l2.z));
-                    p[c + 3] = exp2_mixed<(POLY_OF4 > 0)>(fmaf(p[c + 3], a.scale_log2, -l2.w));
+                    p[c + 0] = exp2_mixed<(poly_of4<T>() > 3)>(fmaf(p[c + 0], a.scale_log2, -l2.x));
+                    p[c + 1] = exp2_mixed<(poly_of4<T>() > 1)>(fmaf(p[c + 1], a.scale_log2, -l2.y));
+                    p[c + 2] = exp2_mixed<(poly_of4<T>() > 2)>(fmaf(p[c + 2], a.scale_log2, -l2.z));
+                    p[c + 3] = exp2_mixed<(poly_of4<T>() > 0)>(fmaf(p[c + 3], a.scale_log2, -l2.w));
                     pk[c4 * 2 + 0] = Pack<T>::two(p[c + 0], p[c + 1]);
                     pk[c4 * 2 + 1] = Pack<T>::two(p[c + 2], p[c + 3]);
                 }
@@ -818,10 +821,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
 #pragma unroll
             for (int c4 = 0; c4 < KQW / 4; ++c4) {
-                p[c4 * 4 + 0] = exp2_mixed<(POLY_OF4 > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2));
-                p[c4 * 4 + 1] = exp2_mixed<(POLY_OF4 > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2));
-                p[c4 * 4 + 2] = exp2_mixed<(POLY_OF4 > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2));
-                p[c4 * 4 + 3] = exp2_mixed<(POLY_OF4 > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2));
+                p[c4 * 4 + 0] = exp2_mixed<(poly_of4<T>() > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2));
+                p[c4 * 4 + 1] = exp2_mixed<(poly_of4<T>() > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2));
+                p[c4 * 4 + 2] = exp2_mixed<(poly_of4<T>() > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2));
+                p[c4 * 4 + 3] = exp2_mixed<(poly_of4<T>() > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2));
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full[st]), (t >> 1) & 1))) { failed = true; break; }
             tc_fence_after_sync();

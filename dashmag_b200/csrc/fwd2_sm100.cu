@@ -57,6 +57,12 @@ template <int HD> struct Geo {
 constexpr int THREADS = 352;
 constexpr int V_WARP = 10;
 constexpr float RESCALE_LOG2 = 8.0f;
+// A row that sees at most this many keys keeps the exact running maximum instead of the lazy one:
+// with few keys one of them often carries most of the weight, and only against the exact maximum is
+// that key's probability exactly 1 before P is rounded to the input dtype - as in the reference's
+// kernels, whose error bounds were measured on such rows.  Long rows, where the weights spread and
+// the roundings average out, keep the lazy maximum and its rare rescales.
+constexpr int EXACT_KEYS = 512;
 
 struct Barriers {
     uint64_t q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
@@ -286,6 +292,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const bool padded = a.mask.kind == 1;
         const float2 sl2 = make_float2(a.scale_log2, a.scale_log2);
         float m_ref = -INFINITY, l = 0.f;
+        const float rescale_at = hi - lo <= EXACT_KEYS ? 0.f : RESCALE_LOG2;
         for (int j = 0; j < steps && !failed; ++j) {
             const int k0 = kmin + j * BN;
             uint32_t pb[BN / 32] = {0, 0, 0, 0};
@@ -322,18 +329,21 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 for (int e = 0; e < 8; ++e)
                     mx8[e] = c + 8 + e < BN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
             const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
-            // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8.
+            // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8 - or by
+            // anything at all, for a row of few keys (see EXACT_KEYS).
             float factor = 1.f;
             bool rescale = false;
             if (m_ref == -INFINITY) {
                 m_ref = mx;  // nothing accumulated yet for this row (or exact zeros)
-            } else if ((mx - m_ref) * a.scale_log2 > RESCALE_LOG2) {
-                factor = ex2((m_ref - mx) * a.scale_log2);
+            } else if ((mx - m_ref) * a.scale_log2 > rescale_at) {
+                // The difference of the two offsets as the exponentials use them (each product rounded on its
+                // own), so that what was summed before and what is summed from here on share one reference.
+                factor = ex2(__fsub_rn(__fmul_rn(m_ref, a.scale_log2), __fmul_rn(mx, a.scale_log2)));
                 l *= factor;
                 m_ref = mx;
                 rescale = true;
             }
-            const float neg = m_ref == -INFINITY ? 0.f : -m_ref * a.scale_log2;
+            const float neg = m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
             const float2 neg2 = make_float2(neg, neg);
 
             // O holds steps 0..j-1 once P V of step j - 1 has completed (it has: S of this step was
@@ -403,7 +413,13 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             // Once per row, so in f64: the product, the logarithm and their sum round once, to f32 at the end.
-            if (row < a.tq) a.lse[base] = l > 0.f ? (float)((double)m_ref * (double)a.scale + log((double)l)) : -INFINITY;
+            // The exponentials were taken against -m_ref * scale_log2 ROUNDED to f32, a factor common to the
+            // whole row that is not in m_ref * scale: its rounding error (in base-2 units) goes back in.
+            if (row < a.tq) {
+                const float used = __fmul_rn(m_ref, a.scale_log2);   // what the loop subtracted from every exponent
+                const double slip = (double)used - (double)m_ref * (double)a.scale_log2;
+                a.lse[base] = l > 0.f ? (float)((double)m_ref * (double)a.scale + slip * 0.6931471805599453 + log((double)l)) : -INFINITY;
+            }
             tc_fence_before_sync();
         } else {
             failed = true;

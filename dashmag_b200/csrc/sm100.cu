@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -63,9 +64,9 @@ bool tma_readable(const void *ptr, const int64_t *stride) {
     return true;
 }
 
-// A [B, T, H, d] tensor of 16-bit elements (d = 128 or 64) as a 4-D map (d, h, t, b) with boxes of
+// A [B, T, H, d] tensor of 16-bit elements (d = 64, 128 or 256) as a 4-D map (d, h, t, b) with boxes of
 // 64 x 1 x 128 x 1 and the 128-byte swizzle: each load brings 128 rows of 128 bytes of one head.
-bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows = 128, int d = 128) {
+bool encode_uncached(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows, int d) {
     EncodeTiled fn = encoder();
     if (!fn) return false;
     auto bytes = [](int64_t elems) { return static_cast<cuuint64_t>(elems) * 2; };
@@ -82,22 +83,73 @@ bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, c
     return r == CUDA_SUCCESS;
 }
 
+// A tensor map is a pure function of the address and the geometry it was encoded from, not of the
+// bytes behind the address, and a training loop or a decoder calls with the same buffers step after
+// step: the last maps are kept, keyed on everything the encoder reads, so that a repeated call costs
+// a lookup instead of a trip through the driver per tensor (short calls are bound by exactly that
+// host time, crates/dash-ops/src/attention.rs:123-127).
+struct MapKey {
+    const void *ptr;
+    int dtype, b, t, h, rows, d;
+    int64_t s0, s1, s2;
+    bool operator==(const MapKey &o) const {
+        return ptr == o.ptr && dtype == o.dtype && b == o.b && t == o.t && h == o.h && rows == o.rows && d == o.d &&
+               s0 == o.s0 && s1 == o.s1 && s2 == o.s2;
+    }
+};
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int MAP_SLOTS = 64, MAP_WAYS = 4;
+MapSlot g_maps[MAP_SLOTS];
+unsigned g_map_turn[MAP_SLOTS / MAP_WAYS];
+std::mutex g_map_mutex;
+std::atomic<uint64_t> g_map_encodes{0};
+
+bool encode(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows = 128, int d = 128) {
+    const MapKey key{ptr, dtype, b, t, h, rows, d, stride[0], stride[1], stride[2]};
+    uint64_t x = reinterpret_cast<uintptr_t>(ptr) >> 4;
+    x ^= (uint64_t)(unsigned)t * 0x9E3779B97F4A7C15ull + (uint64_t)(unsigned)h * 0xC2B2AE3D27D4EB4Full + (uint64_t)(unsigned)(rows + d + dtype);
+    x ^= x >> 29;
+    const int set = (int)(x % (MAP_SLOTS / MAP_WAYS));
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        for (int w = 0; w < MAP_WAYS; ++w) {
+            const MapSlot &s = g_maps[set * MAP_WAYS + w];
+            if (s.used && s.key == key) { *map = s.map; return true; }
+        }
+    }
+    if (!encode_uncached(map, dtype, ptr, b, t, h, stride, rows, d)) return false;
+    g_map_encodes.fetch_add(1, std::memory_order_relaxed);
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    MapSlot &s = g_maps[set * MAP_WAYS + (g_map_turn[set]++ % MAP_WAYS)];
+    s.key = key;
+    s.map = *map;
+    s.used = true;
+    return true;
+}
+
 float resolved_scale(const dash_attn_params *p) {
     return p->has_scale ? p->scale : (float)(1.0 / std::sqrt((double)p->d));
 }
 
 }  // namespace
 
-bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward) {
+uint64_t sm100_tensor_map_encodes() { return g_map_encodes.load(std::memory_order_relaxed); }
+
+bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward, bool any_size) {
     if (backward && !tma_readable(q, p->do_stride)) return false;  // dO's strides; its base is checked at launch
     if (p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16) return false;
     // Head dimension 64 only from 128 queries and 128 keys on: below that there is a single partial
     // tile of queries or of keys (one block per head), the tensor cores gain nothing, and the generic
     // kernels' f32 FMA sums keep the log-sum-exp within the one or two units in the last place that
-    // the reference's records allow at those sizes.
+    // the reference's records allow at those sizes.  (`any_size`, a switch for tests, lifts the size
+    // rule, so that the records themselves can be run through the tensor-core kernels.)
     // Head dimension 256: the one-tile forward only (two accumulators of 256 columns are all of tensor
     // memory, so the backward stays on the generic kernels), under the same size rule.
-    const bool big = p->tq >= 128 && p->tk >= 128;
+    const bool big = any_size || (p->tq >= 128 && p->tk >= 128);
     if (p->d != 128 && !(p->d == 64 && big) && !(p->d == 256 && big && !backward)) return false;
     const float scale = resolved_scale(p);
     if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
@@ -149,12 +201,8 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     bool ok = encode(&m.dq128, p->dtype, a.dq, p->b, p->tq, p->hq, dq_stride, 128, p->d) &&
               encode(&m.q128, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 128, p->d) &&
               encode(&m.do128, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 128, p->d) &&
-              encode(&m.k64, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 64, p->d) &&
-              encode(&m.v64, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 64, p->d) &&
               encode(&m.k128, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 128, p->d) &&
-              encode(&m.v128, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 128, p->d) &&
-              encode(&m.q64, p->dtype, q, p->b, p->tq, p->hq, p->q_stride, 64, p->d) &&
-              encode(&m.do64, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 64, p->d);
+              encode(&m.v128, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 128, p->d);
     if (!ok) {
         err = "attention_backward: the driver refused a TMA tensor map over the inputs";
         return cudaSuccess;

@@ -30,12 +30,10 @@ struct Sm100BwdArgs {
     int *order;          // scratch: the key blocks in order of falling work, [B * ceil(Tk / 128)]
 };
 
-// Tensor maps of the backward: each tensor once with boxes of 128 rows (the tile a block keeps)
-// and once with boxes of 64 rows (the tiles it streams).
+// Tensor maps of the backward: every tensor with boxes of 128 rows, resident or streamed.
 struct Sm100BwdMaps {
-    CUtensorMap q128, do128, k64, v64;   // dq kernel
+    CUtensorMap q128, do128, k128, v128;
     CUtensorMap dq128;                   // dq kernel's output
-    CUtensorMap k128, v128, q64, do64;   // dkdv kernel
 };
 
 // Adds the kernels it launched to *launches.

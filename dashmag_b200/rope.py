@@ -95,9 +95,10 @@ class Rope:
         else:
             p.start, p.period = where["start"], where["period"]
         tables = self.tables()
-        rc = _lib.lib().dash_rope_apply(ctypes.byref(tables), ctypes.byref(p), _ptr(tensors[0]), _ptr(outs[0]),
-                                        _ptr(tensors[1]) if other is not None else None,
-                                        _ptr(outs[1]) if other is not None else None, _stream(x.device))
+        with torch.cuda.device(x.device):   # the library launches on the current device
+            rc = _lib.lib().dash_rope_apply(ctypes.byref(tables), ctypes.byref(p), _ptr(tensors[0]), _ptr(outs[0]),
+                                            _ptr(tensors[1]) if other is not None else None,
+                                            _ptr(outs[1]) if other is not None else None, _stream(x.device))
         if rc != _lib.OK:
             _raise(rc)
         return outs[0] if other is None else (outs[0], outs[1])
@@ -165,11 +166,12 @@ def attention_decode_append_rope(rope: Rope, query, new_key, new_value, key, val
     out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
     ws = _workspace(lib.dash_attn_decode_append_rope_workspace(ctypes.byref(p)), query.device)
     tables = rope.tables()
-    rc = lib.dash_attn_decode_append_rope(ctypes.byref(p), ctypes.byref(tables),
-                                          _ptr(positions.contiguous()) if positions is not None else None,
-                                          positions.element_size() if positions is not None else 0,
-                                          _ptr(query), _ptr(new_key), _ptr(new_value), _ptr(key), _ptr(value), _ptr(out),
-                                          _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
+    with torch.cuda.device(query.device):   # the library launches on the current device
+        rc = lib.dash_attn_decode_append_rope(ctypes.byref(p), ctypes.byref(tables),
+                                              _ptr(positions.contiguous()) if positions is not None else None,
+                                              positions.element_size() if positions is not None else 0,
+                                              _ptr(query), _ptr(new_key), _ptr(new_value), _ptr(key), _ptr(value), _ptr(out),
+                                              _ptr(ws), 0 if ws is None else ws.numel(), _stream(query.device))
     if rc != _lib.OK:
         _raise(rc)
     return out

@@ -72,8 +72,9 @@ def sample(logits: torch.Tensor, options: SampleOptions = SampleOptions(), token
     out = Sampled(torch.empty(b, dtype=token_dtype, device=dev), *(torch.empty(b, dtype=torch.float32, device=dev) for _ in range(3)))
     lib = _lib.lib()
     ws = _workspace(lib.dash_sample_workspace(ctypes.byref(p)), dev)
-    rc = lib.dash_sample(ctypes.byref(p), _ptr(logits), _ptr(out.tokens), _ptr(out.logprob), _ptr(out.tempered_logprob),
-                         _ptr(out.sampling_logprob), _ptr(ws), 0 if ws is None else ws.numel(), _stream(dev))
+    with torch.cuda.device(dev):   # the library launches on the current device
+        rc = lib.dash_sample(ctypes.byref(p), _ptr(logits), _ptr(out.tokens), _ptr(out.logprob), _ptr(out.tempered_logprob),
+                             _ptr(out.sampling_logprob), _ptr(ws), 0 if ws is None else ws.numel(), _stream(dev))
     if rc != _lib.OK:
         _raise(rc)
     return out

@@ -9,7 +9,8 @@
  *
  * Conventions (crates/dash-contract/src/lib.rs, crates/dash-ops/src/attention.rs:85-93):
  *   - every pointer except the parameter structs is DEVICE memory owned by the caller; the library
- *     allocates nothing and keeps nothing between calls; scratch comes in through `workspace`;
+ *     allocates nothing; scratch comes in through `workspace` (dash_attn_decode_static, which uses
+ *     an array of the library's own, is the one exception and says so);
  *   - work is enqueued on `stream` and the call returns without synchronising;
  *   - layouts: q, o, do, dq [B,Tq,Hq,D]; k, v, dk, dv [B,Tk,Hkv,D]; lse [B,Tq,Hq] f32; decode
  *     q / out [B,Hq,D], cache [B,S,Hkv,D], lengths [B];
@@ -22,7 +23,11 @@
  *     dash_attn_last_error() names the operation and the argument, with the reference's own
  *     wording where it panics (crates/dash-ops/src/attention.rs:551-638).  Nothing is launched
  *     when a call is refused.  There is no CPU fallback.
- *   - re-entrant: no mutable global state beyond atomic counters and a thread-local error string.
+ *   - re-entrant.  What the library does keep between calls, all of it process-wide: atomic counters
+ *     (dash_attn_probe), the test switches (dash_attn_force_*), a thread-local error string, a small
+ *     cache of TMA tensor maps keyed on address and geometry (never on contents), one sticky status
+ *     word per device that a bounded wait inside a tensor-core kernel raises when it runs out
+ *     (dash_attn_device_status), and the 16 MiB device array of dash_attn_decode_static.
  */
 #ifndef DASH_ATTN_H
 #define DASH_ATTN_H
@@ -301,12 +306,20 @@ enum {
     DASH_ATTN_PROBE_ATOMIC_RUNS = 3,     /* backward passes that summed dq with atomics */
     DASH_ATTN_PROBE_TENSOR_CORE_RUNS = 4, /* calls that took the tcgen05 path */
     DASH_ATTN_PROBE_GENERIC_RUNS = 5,    /* calls that took the generic kernels */
-    DASH_ATTN_PROBE_COUNT = 6
+    DASH_ATTN_PROBE_TENSOR_MAP_ENCODES = 6, /* TMA tensor maps encoded through the driver (repeated calls reuse theirs) */
+    DASH_ATTN_PROBE_COUNT = 7
 };
 uint64_t dash_attn_probe(int which);
 
 /* For tests: 0 = choose by the call (default), 1 = always the generic kernels. */
 void dash_attn_force_generic(int on);
+/*
+ * For tests: 1 = the tensor-core kernels also take the calls they leave to the generic kernels by
+ * SIZE alone (head dimension 64 or 256 with fewer than 128 queries or keys - a single partial
+ * tile), so that the reference's small recorded cases can be run through them; every other
+ * precondition (dtype, strides, alignment, scale) still decides.  dash_attn_force_generic wins.
+ */
+void dash_attn_force_tensor(int on);
 
 #ifdef __cplusplus
 }

@@ -26,6 +26,26 @@ def test_matches_torch(adapter, dtype, bounds, deterministic):
     print("largest relative errors:", worst)
 
 
+@pytest.mark.parametrize("dtype,bounds", [(DType.BF16, C.BF16), (DType.F16, C.F16)], ids=["bf16", "f16"])
+def test_matches_torch_on_the_tensor_core_kernels(adapter, dtype, bounds):
+    """The same ten records with the size rule lifted (dash_attn_force_tensor), so that the tcgen05
+    kernels themselves meet the reference's recorded vectors, as the reference's fast kernels do:
+    the D = 64 records through the two-tile forward and both backward kernels, the D = 256 record
+    through the one-tile forward (its backward stays where the default path has it).  The bounds
+    are dash-conformance's own (crates/dash-conformance/src/attention.rs:99-108)."""
+    from dashmag_b200 import _lib
+    lib = _lib.lib()
+    before = _lib.probe("tensor_core_runs")
+    lib.dash_attn_force_tensor(1)
+    try:
+        worst = C.matches_torch(adapter, f"b200 tcgen05 {dtype.name.lower()}", dtype, True, bounds).all_ran()
+    finally:
+        lib.dash_attn_force_tensor(0)
+    ran = _lib.probe("tensor_core_runs") - before
+    assert ran >= 19, f"only {ran} of the records' 20 passes ran on the tensor cores"
+    print("largest relative errors on the tensor-core kernels:", worst)
+
+
 def test_forward_without_gradients(adapter):
     C.without_gradients(adapter, "b200", C.AUTOTUNE_F32).all_ran()
 

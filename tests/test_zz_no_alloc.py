@@ -68,6 +68,32 @@ def test_static_scratch_decode_matches_the_workspace_entry_point_twice_in_a_row(
         assert np.all(got[empty] == 0.0)
 
 
+def test_static_scratch_decode_cuts_fewer_longer_splits_when_the_planned_ones_do_not_fit():
+    """64 sequences x 32 query heads on one key-value head, D = 128, a cache of 4096: the plan is 32
+    splits of 128 keys, of which only 15 fit the array (64 * 32 * 129 + 64 floats each), so the call
+    doubles the chunk to 512 keys and runs 8 splits - the multi-unit path of the tensor-core split
+    pass at a chunk the planner itself never picks for this shape."""
+    dev = torch.device("cuda:0")
+    b, s, hq, hkv, d = 64, 4096, 32, 1, 128
+    gen = torch.Generator(device=dev).manual_seed(77)
+    q = torch.randn((b, hq, d), generator=gen, device=dev).to(torch.bfloat16)
+    k = torch.randn((b, s, hkv, d), generator=gen, device=dev).to(torch.bfloat16)
+    v = torch.randn((b, s, hkv, d), generator=gen, device=dev).to(torch.bfloat16)
+    lengths = torch.randint(1, s + 1, (b,), generator=gen, device=dev, dtype=torch.int32)
+    lengths[0], lengths[1] = s, 1
+    got = decode_static(q, k, v, lengths, AttentionOptions())
+    want = A.attention_decode(q, k, v, lengths, AttentionOptions())
+    torch.cuda.synchronize()
+    got, want = got.float().cpu().numpy(), want.float().cpu().numpy()
+    slack = BF16_ROUNDING * np.abs(want) * 1.02 + 2e-6 * np.abs(want).max()
+    assert np.all(np.abs(got - want) <= slack), f"max difference {np.max(np.abs(got - want)):.3e}"
+    rows = [0, 1, 17, 63]   # the oracle on a few sequences: the whole batch is 8 G products
+    sub = lambda t: t[rows].float().cpu().numpy()
+    reference = oracle.decode(sub(q), sub(k), sub(v), lengths=lengths[rows].cpu().numpy())
+    slack = BF16_ROUNDING * np.abs(reference) * 1.02 + 2e-6 * np.abs(reference).max()
+    assert np.all(np.abs(got[rows] - reference) <= slack)
+
+
 def test_static_scratch_decode_refuses_what_does_not_fit():
     """B * Hq * (D + 1) floats of partials per split must fit the 4 Mi-float array."""
     meta = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device="meta")
