@@ -87,6 +87,27 @@ def decode_plan(lengths: Sequence[int], world: int) -> List[List[int]]:
     return balanced_bins([int(n) for n in lengths], world)
 
 
+def training_share(entry, lengths: Sequence[int], q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *more: torch.Tensor):
+    """One rank's part of a packed batch ``[1, T, H, D]`` under a plan entry of :func:`training_plan`:
+    ``(lengths of its sequences, q, k, v, *more)`` with ``more`` cut like ``q`` (the output's
+    gradient, the output).  With every sequence on the rank the parts are head slices of the
+    caller's tensors, read in place through their strides; with a bin of the sequences the bin's
+    tokens are gathered into packed tensors of their own (a rank that owns some of the sequences
+    holds those sequences, not the whole batch)."""
+    seqs, kv, qh = entry
+    lengths = [int(n) for n in lengths]
+    cut_q = [t[:, :, qh] for t in (q,) + tuple(more)]
+    cut_kv = [t[:, :, kv] for t in (k, v)]
+    if list(seqs) != list(range(len(lengths))):
+        starts = [0]
+        for n in lengths:
+            starts.append(starts[-1] + n)
+        tokens = lambda t: (torch.cat([t[:, starts[i]:starts[i + 1]] for i in seqs], dim=1) if len(seqs)
+                            else t[:, :0].contiguous())
+        cut_q, cut_kv = [tokens(t) for t in cut_q], [tokens(t) for t in cut_kv]
+    return ([lengths[i] for i in seqs], cut_q[0], cut_kv[0], cut_kv[1], *cut_q[1:])
+
+
 def shard_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rank: int, world: int):
     """This rank's head slices of ``[B,T,H,D]`` tensors: views, read in place through strides."""
     hkv, group = k.shape[2], q.shape[2] // k.shape[2]

@@ -28,13 +28,15 @@ TILED = {
     DType.F32: [1e-5, 1e-6, 1e-5, 1e-5, 1e-5],
 }
 DECODE = {DType.BF16: 2.2e-3, DType.F16: 2.6e-4, DType.F32: 2e-6}
-# Shapes of this build's own choosing (the reference's bounds are the largest errors it measured at
-# ITS shapes): what the arithmetic allows.  The output's and each gradient's single rounding is up
-# to 2^-8 (bf16) or 2^-11 (f16) of the largest value; P and dS are rounded once more before the
-# second products on the tensor-core path, and delta comes from the rounded output.
+# Shapes of this build's own choosing: the reference's bounds for its tiled shapes again, but for the
+# output (and bf16 dV).  The output's own rounding alone is between 2^-9 and 2^-8 of the LARGEST value
+# (3.9e-3 in bf16, 4.9e-4 in f16), depending on where that value sits between two powers of two, so a
+# bound of 3.3e-3 is a property of the reference's shapes and seeds.  Largest errors measured on the
+# 54 cases below (D = 128, 64, 256; bf16 | f16): o 4.01e-3 | 4.77e-4, lse 2.2e-7, dq 4.78e-3 | 5.96e-4,
+# dk 4.08e-3 | 6.04e-4, dv 4.26e-3 | 4.63e-4.
 OWN = {
-    DType.BF16: [5.0e-3, 1e-6, 8.0e-3, 5.5e-3, 5.0e-3],
-    DType.F16: [6.0e-4, 1e-6, 9.0e-4, 8.0e-4, 6.5e-4],
+    DType.BF16: [4.2e-3, 4.4e-7, 7.7e-3, 4.6e-3, 4.4e-3],
+    DType.F16: [5.0e-4, 4.4e-7, 7.3e-4, 6.8e-4, 4.9e-4],
     DType.F32: [1e-5, 1e-6, 1e-5, 1e-5, 1e-5],
 }
 ROUNDING = {DType.BF16: 2.0 ** -8, DType.F16: 2.0 ** -11, DType.F32: 2e-6}
@@ -114,12 +116,7 @@ def test_head_dimension_256_runs_the_tensor_core_forward(adapter, case, dtype):
     before = _lib.probe("tensor_core_runs")
     got = run_case(adapter, case, dtype)
     assert _lib.probe("tensor_core_runs") == before + 1, "the forward, and only it, ran on the tensor cores"
-    # The f16 output a tenth wider than at D = 128: one-tile steps of 128 keys round P a step at a time
-    # against one lazy maximum per row, and the non-causal shape came out at 6.1e-4.
-    bounds = list(OWN[dtype])
-    if dtype == DType.F16:
-        bounds[0] = 6.6e-4
-    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), bounds)
+    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
     again = run_case(adapter, case, dtype)
     assert np.array_equal(got.out, again.out, equal_nan=True) and np.array_equal(got.lse, again.lse)
 

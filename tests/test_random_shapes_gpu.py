@@ -58,11 +58,12 @@ def random_cases(count, seed, d=128):
 
 
 CASES = random_cases(40, 20261125) + random_cases(20, 20261126, d=64) + random_cases(12, 20261127, d=256)
-# o, lse, dq, dk, dv relative to each result's largest value.  The gradients are sums of products of
-# values rounded to bf16 (P, dS: 2^-9 each), so their error grows with the number of terms and the
-# bounds of the fixed shapes (test_kernels_gpu.OWN) are a quarter too tight for shapes drawn at
-# random; a wrong tile, mask or ordering is off by orders of magnitude more.
-SWEEP = [6.0e-3, 1e-6, 1.0e-2, 7.0e-3, 6.5e-3]
+# o, lse, dq, dk, dv relative to each result's largest value: the bounds of the fixed shapes
+# (test_kernels_gpu.OWN) with a tenth more room for dk, whose sums of values rounded to bf16 (P, dS:
+# 2^-9 each) grow with the number of terms at shapes drawn at random.  Largest errors measured over
+# the 72 cases: 4.35e-3, 2.8e-7, 4.95e-3, 4.99e-3, 3.87e-3; a wrong tile, mask or ordering is off by
+# orders of magnitude more.
+SWEEP = [4.6e-3, 4.4e-7, 7.7e-3, 5.3e-3, 4.4e-3]
 
 
 @pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])

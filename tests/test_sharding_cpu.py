@@ -45,6 +45,28 @@ def test_training_plan_splits_sequences_when_heads_run_out():
     assert all(seqs == list(range(len(lengths))) for seqs, _, _ in plan)
 
 
+def test_training_share_cuts_heads_in_place_and_gathers_sequence_bins():
+    lengths = [5, 3, 7, 2]
+    q = torch.arange(17 * 8 * 2, dtype=torch.float32).reshape(1, 17, 8, 2)
+    k = torch.arange(17 * 2 * 2, dtype=torch.float32).reshape(1, 17, 2, 2)
+    whole = sharding.training_plan(lengths, hkv=2, group=4, world=2)
+    for r, entry in enumerate(whole):
+        ls, qs, ks, vs, gs = sharding.training_share(entry, lengths, q, k, k, q)
+        assert ls == lengths and qs.data_ptr() == q[:, :, 4 * r:].data_ptr() and qs.stride() == q.stride()  # a view
+        assert torch.equal(qs, q[:, :, 4 * r:4 * r + 4]) and torch.equal(ks, k[:, :, r:r + 1]) and torch.equal(gs, qs)
+    bins = sharding.training_plan(lengths, hkv=2, group=4, world=4)   # two ranks per head split the sequences
+    covered = {0: [], 1: []}
+    for entry in bins:
+        seqs, kv, qh = entry
+        ls, qs, ks, vs, gs = sharding.training_share(entry, lengths, q, k, k, q)
+        assert ls == [lengths[i] for i in seqs] and qs.shape == (1, sum(ls), 4, 2) and ks.shape == (1, sum(ls), 1, 2)
+        starts = np.concatenate([[0], np.cumsum(lengths)])
+        want = torch.cat([q[:, starts[i]:starts[i + 1], qh] for i in seqs], dim=1)
+        assert torch.equal(qs, want)
+        covered[kv.start] += list(seqs)
+    assert sorted(covered[0]) == sorted(covered[1]) == [0, 1, 2, 3]
+
+
 def test_decode_plan_balances_cache_lengths():
     rng = np.random.default_rng(3)
     lengths = rng.integers(1024, 32769, size=64)

@@ -85,7 +85,9 @@ def test_static_scratch_decode_cuts_fewer_longer_splits_when_the_planned_ones_do
     want = A.attention_decode(q, k, v, lengths, AttentionOptions())
     torch.cuda.synchronize()
     got, want = got.float().cpu().numpy(), want.float().cpu().numpy()
-    slack = BF16_ROUNDING * np.abs(want) * 1.02 + 2e-6 * np.abs(want).max()
+    # Two roundings of f32 results that differ in their last bits (8 splits against 32) may land on
+    # neighbouring bf16 values: one whole step between the two, half a step from each to the oracle.
+    slack = 2 * BF16_ROUNDING * np.abs(want) * 1.02 + 2e-6 * np.abs(want).max()
     assert np.all(np.abs(got - want) <= slack), f"max difference {np.max(np.abs(got - want)):.3e}"
     rows = [0, 1, 17, 63]   # the oracle on a few sequences: the whole batch is 8 G products
     sub = lambda t: t[rows].float().cpu().numpy()
