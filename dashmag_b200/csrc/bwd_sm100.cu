@@ -51,6 +51,9 @@ constexpr int KQW = QS / KCG;              // columns of a step per elementwise 
 constexpr int KEW_THREADS = 32 * 4 * KCG;
 constexpr int KAUX_WARP = 2 + 4 * KCG;     // dkdv: one more warp gathers the per-query vectors
 constexpr int KTHREADS = 32 * (3 + 4 * KCG);
+constexpr int KRED_WARP = KAUX_WARP + 1;   // fused dkdv: four more warps (one per TMEM lane quadrant) send dQ out
+constexpr int KTHREADS_FUSED = KTHREADS + 128;
+constexpr int RED_SLOT = 128 * 128;        // a staging slot of the dQ reduction: 128 rows of 32 f32 columns
 static_assert(KQW == 32, "one 32-column TMEM load per thread and phase");
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -166,44 +169,74 @@ __device__ __forceinline__ void queries_of_key(const MaskArgs &m, int key, int t
     if (end < first) end = first;
 }
 
-constexpr int CU_CACHE = 768;   // offsets of packed sequences kept in shared memory (dkdv)
+// Offsets of packed sequences kept in shared memory (dkdv); the fused form, whose tiles fill shared
+// memory to the last kilobytes, keeps fewer.
+template <bool FUSED> constexpr int cu_cache() { return FUSED ? 64 : 768; }
 
 }  // namespace
 
 // =================================================================================================
-// Plan: the key blocks of every batch element ordered by falling work
+// Plan: the order in which the (key block, key-value head) units of dkdv are launched
 // =================================================================================================
-// The sweep of a key block is as long as the range of queries that may see it, which under
-// causality and packing differs by two orders of magnitude between blocks; blocks are scheduled in
-// index order, so the order is worth a tiny kernel: one block counts the steps of each key block
-// and ranks them (ties by index, so the order is a pure function of the inputs).
+// Two things decide it.  The sweep of a key block is as long as the range of queries that may see it,
+// which under causality and packing differs by two orders of magnitude between blocks, and blocks are
+// scheduled in index order: long sweeps must start first or the kernel ends in a tail.  And what runs
+// at the same time should touch the same memory: the key blocks of one sequence and one key-value
+// head stream the same Q / dO tiles of that head's group (and, in the fused form, add to the same
+// rows of the f32 dQ accumulator), one tile apart, so that side by side they find each other's tiles
+// in L2 - where all heads of many sequences at once push each other's out.  So: sequences by
+// falling work of their longest sweep; within a sequence one head after the other; within a head the
+// key blocks by falling work.  One block of threads counts the steps of each key block, ranks them
+// and writes, for every launch index, item * hkv + head (ties by index, so the order is a pure
+// function of the inputs).
 constexpr int PLAN_MAX = 2048;
 constexpr int PLAN_THREADS = 1024;
 
 __global__ void __launch_bounds__(PLAN_THREADS) bwd_plan_kernel(const Sm100BwdArgs a, int items) {
-    __shared__ int work[PLAN_MAX];
+    // Items are (batch element, key block) in index order, so the items of one sequence are a run of
+    // consecutive items: the runs are listed once, and each item then ranks its run among the runs
+    // and itself within its run.
+    __shared__ int work[PLAN_MAX], seq[PLAN_MAX], run_top[PLAN_MAX];
+    __shared__ unsigned short run_of[PLAN_MAX], run_first[PLAN_MAX], run_len[PLAN_MAX];   // all below PLAN_MAX
+    __shared__ int runs;
     const int nkb = (a.tk + BIG - 1) / BIG;
+    if (threadIdx.x == 0) runs = 0;
     for (int i = threadIdx.x; i < items; i += PLAN_THREADS) {
-        const int kt = i % nkb, k0 = kt * BIG;
+        const int bi = i / nkb, kt = i - bi * nkb, k0 = kt * BIG;
         int first, end;
         query_range(a.mask, k0, min(k0 + BIG, a.tk), a.tq, a.tk, first, end);
         work[i] = end > first ? (end - first + QS - 1) / QS : 0;
+        // The sequence a key block belongs to: the packed sequence of its first key, else its batch
+        // element (kept apart per batch element so that a run never crosses one).
+        seq[i] = a.mask.kind == 2 ? max(sequence_of(a.mask.cu_k, a.mask.idx_bytes, a.mask.seqs, k0), 0) : bi;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < items; i += PLAN_THREADS) {
-        const int w = work[i];
-        int rank = 0;
-        for (int j = 0; j < items; ++j) {
-            const int x = work[j];
-            rank += (x > w) || (x == w && j < i);
+        if (i == 0 || seq[i - 1] != seq[i]) {   // the head of a run measures it
+            int n = 1, top = work[i];
+            while (i + n < items && seq[i + n] == seq[i]) { top = max(top, work[i + n]); ++n; }
+            const int r = atomicAdd(&runs, 1);
+            run_first[r] = (unsigned short)i;
+            run_len[r] = (unsigned short)n;
+            run_top[r] = top;
+            for (int j = 0; j < n; ++j) run_of[i + j] = (unsigned short)r;
         }
-        a.order[rank] = i;
+    }
+    __syncthreads();
+    const int nruns = runs;
+    for (int i = threadIdx.x; i < items; i += PLAN_THREADS) {
+        const int r = run_of[i], f = run_first[r], n = run_len[r], tp = run_top[r], w = work[i];
+        int before = 0, ahead = 0;   // items of the runs that go first; items of this run ahead of i
+        for (int j = 0; j < nruns; ++j)
+            if (run_top[j] > tp || (run_top[j] == tp && run_first[j] < f)) before += run_len[j];
+        for (int j = f; j < f + n; ++j) ahead += (work[j] > w) || (work[j] == w && j < i);
+        for (int hk = 0; hk < a.hkv; ++hk) a.order[before * a.hkv + hk * n + ahead] = i * a.hkv + hk;
     }
 }
 
-size_t bwd_sm100_order_bytes(int b, int tk) {
-    const long long items = (long long)b * ((tk + BIG - 1) / BIG);
-    return (size_t)((items * 4 + 255) & ~255LL);
+size_t bwd_sm100_order_bytes(int b, int tk, int hkv) {
+    const long long units = (long long)b * ((tk + BIG - 1) / BIG) * hkv;
+    return (size_t)((units * 4 + 255) & ~255LL);
 }
 
 // =================================================================================================
@@ -218,12 +251,27 @@ size_t bwd_sm100_order_bytes(int b, int tk) {
 //     dV(t)  S^T(t+1)  dK(t)  dP^T(t+1)
 // so the P half of the elementwise work of step t+1 runs under dK(t) and dP^T(t+1), and its dS half
 // under dV(t+1) and S^T(t+2).
+//
+// The FUSED form (AttentionOptions::deterministic off; the reference's backward_kernel with atomics,
+// crates/dash-ops/src/attention/kernels.rs:1600) adds the fifth product to the same sweep, so that no
+// dq kernel runs and the scores are computed once: dS^T is also written, in the input dtype, to a tile
+// in shared memory, dQ(t) = dS K comes from it (A = dS, MN-major, straight from that tile; B = the
+// resident K) into the columns dP^T has just left, and four more warps take dQ(t) out of tensor memory,
+// stage it 32 columns at a time in shared memory and add it to an f32 accumulator in global memory
+// with bulk tensor reductions (cp.reduce.async.bulk, whole lines added in L2) - in whatever order the
+// key blocks get there, which is what makes this form's dQ differ in its last bits from run to run.
+// Issue order per step t:
+//     dV(t)  S^T(t+1)  dK(t)  dQ(t)  dP^T(t+1)
+// dK(t) reads dS^T from the dP^T columns before dQ(t) overwrites them (MMAs execute in issue order).
+// Shared memory: the dO ring gives up a stage for the dS tile and the staging slots (a dO tile is
+// dead once dV has read it, and the next one is not needed before S^T, dK and dQ have run).
 struct DkdvBarriers {
     uint64_t res_full;
     uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
     uint64_t aux_full[2];
     uint64_t s_full, p_full[2], dp_full, ds_full[2];   // P^T and dS^T arrive in two halves (even, odd k-steps)
     uint64_t acc_ready;
+    uint64_t dq_done, dq_taken;   // fused: dQ(t) is in tensor memory; the reduction warps have taken it out
 };
 
 struct alignas(16) QAux {   // what the elementwise threads need per query of a step
@@ -231,38 +279,49 @@ struct alignas(16) QAux {   // what the elementwise threads need per query of a 
     float delta[QS];
 };
 
-struct DkdvTail {
+template <bool FUSED> struct DkdvTail {
     DkdvBarriers bar;
     QAux aux[2];
     uint32_t tmem_base;
     unsigned int abort;
-    int cu_q[CU_CACHE], cu_k[CU_CACHE];   // the packed sequences' offsets, when they fit
+    int cu_q[cu_cache<FUSED>()], cu_k[cu_cache<FUSED>()];   // the packed sequences' offsets, when they fit
 };
 
-constexpr size_t DKDV_TAIL = 12288;
-static_assert(sizeof(DkdvTail) <= DKDV_TAIL, "the tail of the dkdv kernel's shared memory");
-// 1 KiB slack | K, V resident (2 x 32 KiB) | Q ring 2 x 32 KiB | dO ring 2 x 32 KiB | tail
-template <int HD> constexpr size_t smem_dkdv() { return 1024 + 6 * tile_bytes<HD>() + DKDV_TAIL; }
+template <bool FUSED> constexpr size_t dkdv_tail() { return FUSED ? 3072 : 12288; }
+static_assert(sizeof(DkdvTail<false>) <= dkdv_tail<false>() && sizeof(DkdvTail<true>) <= dkdv_tail<true>(),
+              "the tail of the dkdv kernel's shared memory");
+// 1 KiB slack | K, V resident (2 x 32 KiB) | Q ring 2 x 32 KiB | dO ring 2 x 32 KiB | tail, or fused
+// (no slack: at D = 128 the tiles and the tail are the 227 KiB a block may have, and the kernel checks
+// that its shared memory starts on a 1 KiB boundary)
+//             K, V resident | Q ring 2 | dO 1 | dS^T tile 32 KiB | 2 staging slots of 16 KiB | tail
+template <int HD, bool FUSED> constexpr size_t smem_dkdv() {
+    return FUSED ? 5 * tile_bytes<HD>() + BIG * BIG * 2 + 2 * RED_SLOT + dkdv_tail<true>()
+                 : 1024 + 6 * tile_bytes<HD>() + dkdv_tail<false>();
+}
 
-template <typename T, int HD>
-__global__ void __launch_bounds__(KTHREADS, 1)
+template <typename T, int HD, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? KTHREADS_FUSED : KTHREADS, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                      const Sm100BwdArgs a) {
-    extern __shared__ uint8_t smem_raw[];
+                      const __grid_constant__ CUtensorMap tm_dq_acc, const Sm100BwdArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int BIG_BYTES = tile_bytes<HD>();
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int DOS = FUSED ? 1 : 2;        // stages of the dO ring
+    uint8_t *smem = FUSED ? smem_raw : reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *k_s = smem, *v_s = k_s + BIG_BYTES;
     uint8_t *q_s = v_s + BIG_BYTES;           // [2][BIG_BYTES]
-    uint8_t *do_s = q_s + 2 * BIG_BYTES;      // [2][BIG_BYTES]
-    DkdvTail &sh = *reinterpret_cast<DkdvTail *>(do_s + 2 * BIG_BYTES);
+    uint8_t *do_s = q_s + 2 * BIG_BYTES;      // [DOS][BIG_BYTES]
+    uint8_t *ds_s = do_s + DOS * BIG_BYTES;   // fused: dS^T of the step, [2 halves of 64 queries][128 keys][128 bytes]
+    uint8_t *red_s = ds_s + BIG * BIG * 2;    // fused: [2][RED_SLOT]
+    using Tail = DkdvTail<FUSED>;
+    Tail &sh = *reinterpret_cast<Tail *>(FUSED ? red_s + 2 * RED_SLOT : do_s + DOS * BIG_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Key blocks are taken in the order the plan kernel left: the ones most queries see first, so
-    // that the longest sweeps start early and the short ones fill the tail.
+    // Units are taken in the order the plan kernel left (without one: in index order, the heads of a
+    // key block side by side).
     const int nkb = (a.tk + BIG - 1) / BIG;
-    const int rank = blockIdx.x / a.hkv, hk = blockIdx.x - rank * a.hkv;   // the heads of one key block side by side
-    const int item = a.order ? a.order[rank] : rank;
+    const int unit = a.order ? a.order[blockIdx.x] : (int)blockIdx.x;
+    const int item = unit / a.hkv, hk = unit - item * a.hkv;
     const int b = item / nkb, kt = item - b * nkb;
     const int group = a.hq / a.hkv;
     const int k0 = kt * BIG, k1 = min(k0 + BIG, a.tk);
@@ -270,6 +329,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     if (threadIdx.x == 0) {
         sh.abort = *reinterpret_cast<volatile unsigned int *>(&g_sm100_bwd_status);
+        // The fused form has no room to realign: a window that does not start on a 1 KiB boundary
+        // (the swizzled tiles need it) is reported like a wait that ran out, and nothing runs.
+        if (FUSED && (smem_u32(smem_raw) & 1023u) != 0) sh.abort = 1u;
         mbar_init(BAR(sh.bar.res_full), 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(BAR(sh.bar.q_full[i]), 1);
@@ -285,11 +347,14 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         mbar_init(BAR(sh.bar.ds_full[0]), 4 * KCG);
         mbar_init(BAR(sh.bar.ds_full[1]), 4 * KCG);
         mbar_init(BAR(sh.bar.acc_ready), 1);
+        mbar_init(BAR(sh.bar.dq_done), 1);
+        mbar_init(BAR(sh.bar.dq_taken), 4);          // one arrival per reduction warp
         fence_mbar_init();
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_do);
+        if constexpr (FUSED) prefetch_tensormap(&tm_dq_acc);
         // The resident tiles are on their way before the block knows which queries it sweeps: their
         // flight covers the rest of the setup.  (A block that turns out to have nothing to do waits
         // for them at the end: shared memory must not be written behind a block that has left.)
@@ -310,7 +375,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // sequences' offsets: from shared memory when they fit, so that it costs tens of cycles a probe
     // instead of a trip to L2.
     MaskArgs qmask = a.mask;
-    if (a.mask.kind == 2 && a.mask.seqs + 1 <= CU_CACHE) {
+    if (a.mask.kind == 2 && a.mask.seqs + 1 <= cu_cache<FUSED>()) {
         for (int i = threadIdx.x; i <= a.mask.seqs; i += blockDim.x) {
             sh.cu_q[i] = load_index(a.mask.cu_q, a.mask.idx_bytes, i);
             sh.cu_k[i] = load_index(a.mask.cu_k, a.mask.idx_bytes, i);
@@ -343,8 +408,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 mbar_expect_tx(qf, BIG_BYTES);
                 tma_load_4d(qd, &tm_q, qf, 0, h, q0, b);
                 if constexpr (HD > 64) tma_load_4d(qd + BIG_HALF, &tm_q, qf, 64, h, q0, b);
-                if (!mbar_wait(BAR(sh.bar.do_empty[st]), ph ^ 1)) { failed = true; break; }
-                const uint32_t gf = BAR(sh.bar.do_full[st]), gd = smem_u32(do_s + st * BIG_BYTES);
+                const int gst = t % DOS, gph = (t / DOS) & 1;
+                if (!mbar_wait(BAR(sh.bar.do_empty[gst]), gph ^ 1)) { failed = true; break; }
+                const uint32_t gf = BAR(sh.bar.do_full[gst]), gd = smem_u32(do_s + gst * BIG_BYTES);
                 mbar_expect_tx(gf, BIG_BYTES);
                 tma_load_4d(gd, &tm_do, gf, 0, h, q0, b);
                 if constexpr (HD > 64) tma_load_4d(gd + BIG_HALF, &tm_do, gf, 64, h, q0, b);
@@ -399,6 +465,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             constexpr uint32_t IDESC_SC = idesc_f16(BIG, QS, Pack<T>::FMT, 0, 0);     // [128 keys x 128 queries]
             constexpr uint32_t IDESC_ACC = idesc_f16(BIG, HD, Pack<T>::FMT, 0, 1);    // [128 keys x 128 d], B MN-major
             const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s), 16, 1024), v_desc = smem_desc_sw128(smem_u32(v_s), 16, 1024);
+            // Fused: dQ = dS K with both operands MN-major: A = the dS^T tile (rows = keys = the product's K
+            // dimension, 64 queries to a 128-byte row, the second 64 queries BIG_HALF further on), B = the
+            // resident K read along its rows.
+            constexpr uint32_t IDESC_DQ = idesc_f16(QS, HD, Pack<T>::FMT, 1, 1);   // [128 queries x HD]
+            const uint64_t ds_desc = smem_desc_sw128(smem_u32(ds_s), BIG_HALF, 1024), k_mn = smem_desc_sw128(smem_u32(k_s), BIG_HALF, 1024);
             // The 16 queries of k-step ks of a gradient product, as 16-bit pairs in tensor memory.
             auto a_cols = [](int ks) { return static_cast<uint32_t>(32 * (ks >> 1) + 8 * (ks & 1)); };
             auto scores = [&](int t) -> bool {   // S^T(t) = K Q^T
@@ -418,7 +489,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 return true;
             };
             auto dscores = [&](int t) -> bool {  // dP^T(t) = V dO^T
-                const int st = t & 1, ph = (t >> 1) & 1;
+                const int st = t % DOS, ph = (t / DOS) & 1;
+                // Fused: dQ(t - 1) sits in these columns until the reduction warps have taken it out.
+                if (FUSED && t > 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dq_taken), (t - 1) & 1))) return false;
                 if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.do_full[st]), ph))) return false;
                 tc_fence_after_sync();
                 const uint64_t gk = smem_desc_sw128(smem_u32(do_s + st * BIG_BYTES), 16, 1024);
@@ -441,8 +514,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 // elementwise thread's columns) as soon as they are written, the odd ones behind the
                 // second half; the dO stage is free behind it.
                 {
-                    const uint64_t gm = smem_desc_sw128(smem_u32(do_s + st * BIG_BYTES), BIG_HALF, 1024);
-                    const uint32_t e = BAR(sh.bar.do_empty[st]);
+                    const uint64_t gm = smem_desc_sw128(smem_u32(do_s + (t % DOS) * BIG_BYTES), BIG_HALF, 1024);
+                    const uint32_t e = BAR(sh.bar.do_empty[t % DOS]);
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[half]), ph))) { failed = true; break; }
@@ -478,10 +551,65 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                     }
                     if (failed) break;
                 }
+                if constexpr (FUSED) {
+                    // dQ(t) = dS K over the step's 128 keys, into the columns of dP^T: both halves of dS^T
+                    // are in the shared-memory tile (the waits of dK above), dK(t) has been issued.
+                    if (elect_one()) {
+#pragma unroll
+                        for (int ks = 0; ks < BIG / 16; ++ks)
+                            umma_f16(tmem + COL_DPT, desc_at(ds_desc, ks * 2048), desc_at(k_mn, ks * 2048), IDESC_DQ, ks > 0 ? 1u : 0u);
+                        umma_commit(BAR(sh.bar.dq_done));
+                    }
+                    __syncwarp();
+                }
                 if (t + 1 < steps && !dscores(t + 1)) { failed = true; break; }
             }
             if (!failed && elect_one()) umma_commit(BAR(sh.bar.acc_ready));
         }
+    } else if (FUSED && warp >= KRED_WARP) {
+        // ---------------- fused: dQ(t) out of tensor memory and into the f32 accumulator ----------------
+        // A thread owns a query row (TMEM lane); 64 columns at a time go through the two staging slots
+        // (the layout of a 128-byte-swizzled TMA box of 32 f32 columns x 128 rows) and leave as two
+        // bulk tensor reductions, which add whole lines in L2 and drop rows past the last query.
+        const int lane_base = 32 * (warp & 3), r = lane_base + lane;
+        const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
+        const bool issuer = warp == KRED_WARP && lane == 0;
+        for (int t = 0; t < steps && !failed; ++t) {
+            const int h = hk * group + t / tiles, q0 = qfirst + (t % tiles) * QS;
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dq_done), t & 1))) { failed = true; break; }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int pair = 0; pair < HD / 64; ++pair) {
+                uint32_t x[2][32];
+                tmem_ld32(t_lane + COL_DPT + pair * 64, x[0]);
+                tmem_ld32(t_lane + COL_DPT + pair * 64 + 32, x[1]);
+                tmem_ld_wait();
+                if (pair == HD / 64 - 1) {   // all of dQ(t) is in registers or staged: dP^T(t+1) may overwrite it
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(sh.bar.dq_taken));
+                }
+                // The slots are free once the reductions issued from them have read them.
+                if (issuer) tma_store_wait_read();
+                named_barrier(1, 128);
+#pragma unroll
+                for (int sl = 0; sl < 2; ++sl) {
+                    uint8_t *row = red_s + sl * RED_SLOT + r * 128;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        *reinterpret_cast<uint4 *>(row + ((e ^ (r & 7)) << 4)) =
+                            make_uint4(x[sl][4 * e + 0], x[sl][4 * e + 1], x[sl][4 * e + 2], x[sl][4 * e + 3]);
+                }
+                fence_proxy_async_smem();
+                named_barrier(1, 128);
+                if (issuer) {
+                    tma_reduce_add_4d(&tm_dq_acc, smem_u32(red_s), pair * 64, h, q0, b);
+                    tma_reduce_add_4d(&tm_dq_acc, smem_u32(red_s + RED_SLOT), pair * 64 + 32, h, q0, b);
+                    tma_store_commit();
+                }
+            }
+        }
+        if (issuer) tma_store_wait_read();   // shared memory must not go while a reduction still reads it
     } else {
         // ---------------- elementwise: a key row and 32 of the step's queries per thread ----------------
         const int lane_base = 32 * (warp & 3);
@@ -552,6 +680,20 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                         dk[c4 * 2 + 1] = Pack<T>::two(p[c + 2] * (dp[c + 2] - dl.z), p[c + 3] * (dp[c + 3] - dl.w));
                     }
                     tmem_st8(t_lane + COL_DPT + col0 + half * (KQW / 4), dk);   // dS^T likewise, in the same two halves
+                    if constexpr (FUSED) {
+                        // ... and into the shared-memory tile dQ reads it from: this key's row of the 64-query
+                        // half that holds the thread's columns, two 16-byte chunks of 8 queries, XOR-swizzled by
+                        // the row like a TMA tile.  The tile is free: dQ of the step before was issued ahead of
+                        // this step's dP^T, whose completion (awaited above) means every earlier MMA has completed.
+                        uint8_t *ds_row = ds_s + (cg >> 1) * BIG_HALF + r * 128;
+#pragma unroll
+                        for (int e2 = 0; e2 < 2; ++e2) {
+                            const int chunk = (cg & 1) * 4 + half * 2 + e2;
+                            *reinterpret_cast<uint4 *>(ds_row + ((chunk ^ (r & 7)) << 4)) =
+                                make_uint4(dk[4 * e2 + 0], dk[4 * e2 + 1], dk[4 * e2 + 2], dk[4 * e2 + 3]);
+                        }
+                        fence_proxy_async_smem();
+                    }
                     tmem_st_wait();
                     tc_fence_before_sync();
                     __syncwarp();
@@ -896,19 +1038,51 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
 }
 
+// =================================================================================================
+// The fused form's finish: the f32 accumulator, scaled, in the gradient's dtype
+// =================================================================================================
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_dq_finish_kernel(const float *__restrict__ acc, T *__restrict__ dq, float scale, long long n8) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // eight elements per thread
+    if (i >= n8) return;
+    const float4 lo = reinterpret_cast<const float4 *>(acc)[2 * i], hi = reinterpret_cast<const float4 *>(acc)[2 * i + 1];
+    uint4 v;
+    v.x = Pack<T>::two(lo.x * scale, lo.y * scale);
+    v.y = Pack<T>::two(lo.z * scale, lo.w * scale);
+    v.z = Pack<T>::two(hi.x * scale, hi.y * scale);
+    v.w = Pack<T>::two(hi.z * scale, hi.w * scale);
+    reinterpret_cast<uint4 *>(dq)[i] = v;
+}
+
 // -------------------------------------------------------------------------------------------------
+template <typename T, int HD, bool FUSED>
+static cudaError_t launch_dkdv(const Sm100BwdMaps &m, const Sm100BwdArgs &a, long long items, cudaStream_t stream) {
+    constexpr size_t smem = smem_dkdv<HD, FUSED>();
+    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T, HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dim3 gk((unsigned)(items * a.hkv), 1, 1);
+    bwd_dkdv_sm100_kernel<T, HD, FUSED><<<gk, FUSED ? KTHREADS_FUSED : KTHREADS, smem, stream>>>(m.k128, m.v128, m.q128, m.do128, m.dq_acc, a);
+    return cudaGetLastError();
+}
+
 template <typename T, int HD>
 static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t stream, int *launches) {
-    cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkdv<HD>());
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq<HD>());
-    if (e != cudaSuccess) return e;
-    dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
-    bwd_dq_sm100_kernel<T, HD><<<gq, DQ_THREADS, smem_dq<HD>(), stream>>>(m.q128, m.do128, m.k128, m.v128, m.dq128, a);
-    *launches += 1;
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    const bool fused = a.dq_acc != nullptr;
+    cudaError_t e;
+    const long long dq_elems = (long long)a.b * a.tq * a.hq * HD;
+    if (fused) {
+        // The accumulator starts at zero; every key block adds its share as it gets there.
+        if ((e = cudaMemsetAsync(a.dq_acc, 0, sizeof(float) * (size_t)dq_elems, stream)) != cudaSuccess) return e;
+    } else {
+        e = cudaFuncSetAttribute(bwd_dq_sm100_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq<HD>());
+        if (e != cudaSuccess) return e;
+        dim3 gq(a.hq, (a.tq + BIG - 1) / BIG, a.b);
+        bwd_dq_sm100_kernel<T, HD><<<gq, DQ_THREADS, smem_dq<HD>(), stream>>>(m.q128, m.do128, m.k128, m.v128, m.dq128, a);
+        *launches += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
     const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);
-    if (a.order && items > 1 && items <= PLAN_MAX) {
+    if (a.order && items > 1 && items <= PLAN_MAX && items * a.hkv <= 0x7fffffffLL / 4) {
         bwd_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(a, (int)items);
         *launches += 1;
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
@@ -916,11 +1090,16 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t 
         a.order = nullptr;  // too many to rank in one block (or nothing to rank): index order
     }
     if (items * a.hkv > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    dim3 gk((unsigned)(items * a.hkv), 1, 1);
-    bwd_dkdv_sm100_kernel<T, HD><<<gk, KTHREADS, smem_dkdv<HD>(), stream>>>(m.k128, m.v128, m.q128, m.do128, a);
+    e = fused ? launch_dkdv<T, HD, true>(m, a, items, stream) : launch_dkdv<T, HD, false>(m, a, items, stream);
+    *launches += 1;
+    if (e != cudaSuccess || !fused) return e;
+    const long long n8 = dq_elems / 8;
+    bwd_dq_finish_kernel<T><<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(a.dq_acc, static_cast<T *>(a.dq), a.scale, n8);
     *launches += 1;
     return cudaGetLastError();
 }
+
+size_t bwd_sm100_fused_shared_bytes(int d) { return d == 64 ? smem_dkdv<64, true>() : smem_dkdv<128, true>(); }
 
 cudaError_t read_sm100_bwd_status(unsigned int *status, bool clear) {
     cudaError_t e = cudaMemcpyFromSymbol(status, g_sm100_bwd_status, sizeof(unsigned int));

@@ -66,18 +66,21 @@ bool tma_readable(const void *ptr, const int64_t *stride) {
 
 // A [B, T, H, d] tensor of 16-bit elements (d = 64, 128 or 256) as a 4-D map (d, h, t, b) with boxes of
 // 64 x 1 x 128 x 1 and the 128-byte swizzle: each load brings 128 rows of 128 bytes of one head.
+// (dtype DASH_ATTN_F32: the fused backward's accumulator, 32 f32 columns to a 128-byte box row.)
 bool encode_uncached(CUtensorMap *map, int dtype, const void *ptr, int b, int t, int h, const int64_t *stride, int rows, int d) {
     EncodeTiled fn = encoder();
     if (!fn) return false;
-    auto bytes = [](int64_t elems) { return static_cast<cuuint64_t>(elems) * 2; };
+    const bool f32 = dtype == DASH_ATTN_F32;
+    auto bytes = [f32](int64_t elems) { return static_cast<cuuint64_t>(elems) * (f32 ? 4 : 2); };
     cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)h, (cuuint64_t)t, (cuuint64_t)b};
     // A dimension of extent 1 never moves: give it any legal stride.
     cuuint64_t strides[3] = {h > 1 ? bytes(stride[2]) : 256, t > 1 ? bytes(stride[1]) : 256, b > 1 ? bytes(stride[0]) : 256};
     for (cuuint64_t s : strides)
         if (s == 0 || s % 16 != 0 || s >= (1ull << 40)) return false;
-    cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+    cuuint32_t box[4] = {f32 ? 32u : 64u, 1, (cuuint32_t)rows, 1};
     cuuint32_t elem[4] = {1, 1, 1, 1};
-    CUtensorMapDataType dt = dtype == DASH_ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMapDataType dt = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == DASH_ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -161,7 +164,15 @@ bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const 
 }
 
 size_t sm100_forward_workspace(const dash_attn_params *) { return 0; }
-size_t sm100_backward_workspace(const dash_attn_params *p) { return bwd_sm100_order_bytes(p->b, p->tk); }
+// Whether a backward call takes the five-product form that adds dQ by reductions in L2: only when the
+// caller gave up the fixed order of summation, and only where that form exists (D = 64, 128).
+static bool fused_backward(const dash_attn_params *p) { return !p->deterministic && (p->d == 128 || p->d == 64); }
+static size_t dq_acc_bytes(const dash_attn_params *p) {
+    return (sizeof(float) * (size_t)p->b * p->tq * p->hq * p->d + 255) & ~size_t(255);
+}
+size_t sm100_backward_workspace(const dash_attn_params *p) {
+    return bwd_sm100_order_bytes(p->b, p->tk, p->hkv) + (fused_backward(p) ? dq_acc_bytes(p) : 0);
+}
 
 cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *, cudaStream_t stream, int *launches,
                           std::string &err) {
@@ -194,8 +205,10 @@ cudaError_t sm100_forward(const dash_attn_params *p, const TrainArgs &a, void *,
 
 cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *workspace, cudaStream_t stream, int *launches,
                            bool *atomic, std::string &err) {
-    *atomic = false;  // both kernels sum in a fixed order whatever `deterministic` says
+    const bool fused = fused_backward(p);
+    *atomic = fused;
     Sm100BwdMaps m;
+    float *dq_acc = fused ? reinterpret_cast<float *>(static_cast<char *>(workspace) + bwd_sm100_order_bytes(p->b, p->tk, p->hkv)) : nullptr;
     const void *q = a.q.ptr, *k = a.k.ptr, *v = a.v.ptr, *g = a.dout.ptr;
     const int64_t dq_stride[4] = {(int64_t)p->tq * p->hq * p->d, (int64_t)p->hq * p->d, p->d, 1};   // the gradients are contiguous
     bool ok = encode(&m.dq128, p->dtype, a.dq, p->b, p->tq, p->hq, dq_stride, 128, p->d) &&
@@ -203,6 +216,8 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
               encode(&m.do128, p->dtype, g, p->b, p->tq, p->hq, p->do_stride, 128, p->d) &&
               encode(&m.k128, p->dtype, k, p->b, p->tk, p->hkv, p->k_stride, 128, p->d) &&
               encode(&m.v128, p->dtype, v, p->b, p->tk, p->hkv, p->v_stride, 128, p->d);
+    if (ok && fused) ok = encode(&m.dq_acc, DASH_ATTN_F32, dq_acc, p->b, p->tq, p->hq, dq_stride, 128, p->d);
+    else if (ok) m.dq_acc = m.dq128;   // not read
     if (!ok) {
         err = "attention_backward: the driver refused a TMA tensor map over the inputs";
         return cudaSuccess;
@@ -218,6 +233,7 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     f.dq = a.dq; f.dk = a.dk; f.dv = a.dv;
     f.mask = a.mask;
     f.order = static_cast<int *>(workspace);
+    f.dq_acc = dq_acc;
     return launch_bwd_sm100(p->dtype, m, f, stream, launches);
 }
 

@@ -27,18 +27,21 @@ struct Sm100BwdArgs {
     const float *delta;  // [B,Tq,Hq], rowsum(dO * O)
     void *dq, *dk, *dv;  // contiguous, the inputs' dtype
     MaskArgs mask;
-    int *order;          // scratch: the key blocks in order of falling work, [B * ceil(Tk / 128)]
+    int *order;          // scratch: the (key block, key-value head) units in launch order, [B * ceil(Tk / 128) * Hkv]
+    float *dq_acc;       // scratch [B,Tq,Hq,D] f32, or null: the query gradient summed by reductions in L2 (the fused form)
 };
 
 // Tensor maps of the backward: every tensor with boxes of 128 rows, resident or streamed.
 struct Sm100BwdMaps {
     CUtensorMap q128, do128, k128, v128;
     CUtensorMap dq128;                   // dq kernel's output
+    CUtensorMap dq_acc;                  // the fused form's f32 accumulator, boxes of 32 columns x 128 rows
 };
 
 // Adds the kernels it launched to *launches.
 cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream, int *launches);
-size_t bwd_sm100_order_bytes(int b, int tk);
+size_t bwd_sm100_order_bytes(int b, int tk, int hkv);
+size_t bwd_sm100_fused_shared_bytes(int d);
 
 cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
                              const Sm100FwdArgs &a, cudaStream_t stream);

@@ -102,6 +102,15 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t sr
         ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// One 4-D tile of f32 (or whatever the map's type is), this block's shared memory ADDED to global
+// memory: the reduction runs in L2, a line at a time; rows and columns past the tensor's extents are
+// dropped.  Completion in bulk groups, like a store.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
