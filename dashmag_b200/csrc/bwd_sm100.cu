@@ -25,6 +25,7 @@
 // they were issued early).  Every mbarrier wait is bounded (sm100_ptx.cuh).
 #include <cuda.h>
 
+#include "bwd_common.cuh"
 #include "common.cuh"
 #include "sm100.h"
 #include "sm100_kernels.h"
@@ -60,22 +61,6 @@ constexpr float LOG2E = 1.4426950408889634f;
 // 2^x on the special-function pipe or, for a share of the elements, on the FMA pipe.
 template <bool POLY> __device__ __forceinline__ float exp2_mixed(float x) { return POLY ? ex2_poly3(x) : ex2(x); }
 
-template <typename T> struct Pack;
-template <> struct Pack<__nv_bfloat16> {
-    static constexpr int FMT = 1;
-    static __device__ __forceinline__ uint32_t two(float a, float b) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-        return *reinterpret_cast<uint32_t *>(&v);
-    }
-};
-template <> struct Pack<__half> {
-    static constexpr int FMT = 0;
-    static __device__ __forceinline__ uint32_t two(float a, float b) {
-        __half2 v = __floats2half2_rn(a, b);
-        return *reinterpret_cast<uint32_t *>(&v);
-    }
-};
-
 // Of every four exponentials, how many run on the FMA pipe (ex2_poly3): one for bf16, whose rounding step
 // (2^-9) is thirty times the cubic's error; none for f16, whose step (2^-12) is only four times it.
 template <typename T> constexpr int poly_of4() { return Pack<T>::FMT == 1 ? 1 : 0; }
@@ -110,63 +95,6 @@ __device__ __forceinline__ void store_zero_cols(T *dst) {
     const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) reinterpret_cast<uint4 *>(dst)[c] = z;
-}
-
-// The queries [first, end) that may see some key of [k0, k1): a superset cut from the closed form
-// of the visible interval (query i of a sequence sees key c iff
-// c - right - (Lk - Lq) <= i <= c + left - (Lk - Lq)); exact masking happens per element.
-__device__ __forceinline__ void query_range(const MaskArgs &m, int k0, int k1, int tq, int tk, int &first, int &end) {
-    first = 0;
-    end = 0;
-    if (k1 <= k0) return;
-    if (m.kind == 2) {
-        if (m.seqs <= 0) return;
-        int sa = sequence_of(m.cu_k, m.idx_bytes, m.seqs, k0);
-        int sb = sequence_of(m.cu_k, m.idx_bytes, m.seqs, k1 - 1);
-        if (sb < 0 || sa >= m.seqs) return;
-        sa = max(sa, 0);
-        sb = min(sb, m.seqs - 1);
-        const int qa0 = load_index(m.cu_q, m.idx_bytes, sa), qa1 = load_index(m.cu_q, m.idx_bytes, sa + 1);
-        const int ka0 = load_index(m.cu_k, m.idx_bytes, sa), ka1 = load_index(m.cu_k, m.idx_bytes, sa + 1);
-        const int qb0 = load_index(m.cu_q, m.idx_bytes, sb), qb1 = load_index(m.cu_q, m.idx_bytes, sb + 1);
-        const int kb0 = load_index(m.cu_k, m.idx_bytes, sb), kb1 = load_index(m.cu_k, m.idx_bytes, sb + 1);
-        const int off_a = (ka1 - ka0) - (qa1 - qa0), off_b = (kb1 - kb0) - (qb1 - qb0);
-        first = qa0 + min(max(k0 - ka0 - m.right - off_a, 0), qa1 - qa0);
-        end = qb0 + min(max(k1 - 1 - kb0 + m.left - off_b + 1, 0), qb1 - qb0);
-    } else {
-        const int off = tk - tq;
-        first = min(max(k0 - m.right - off, 0), tq);
-        end = min(max(k1 - 1 + m.left - off + 1, 0), tq);
-    }
-    first = min(max(first, 0), tq);
-    end = min(max(end, 0), tq);
-    if (end < first) end = first;
-}
-
-// The queries [first, end) that see key `key`: the inverse of the visible interval (both ends of a
-// query's interval grow with the query, so the queries that see one key are an interval as well),
-// from the same closed form as query_range and exact.  Key padding is the caller's to apply.
-__device__ __forceinline__ void queries_of_key(const MaskArgs &m, int key, int tq, int tk, int &first, int &end) {
-    first = 0;
-    end = 0;
-    if (key < 0 || key >= tk) return;
-    if (m.kind == 2) {
-        const int s = sequence_of(m.cu_k, m.idx_bytes, m.seqs, key);
-        if (s < 0 || s >= m.seqs) return;
-        const int q0 = load_index(m.cu_q, m.idx_bytes, s), q1 = load_index(m.cu_q, m.idx_bytes, s + 1);
-        const int k0 = load_index(m.cu_k, m.idx_bytes, s), k1 = load_index(m.cu_k, m.idx_bytes, s + 1);
-        if (key >= k1) return;   // between sequences
-        const int off = (k1 - k0) - (q1 - q0), rel = key - k0;
-        first = max(q0, q0 + rel - m.right - off);
-        end = min(q1, q0 + rel + m.left - off + 1);
-    } else {
-        const int off = tk - tq;
-        first = max(0, key - m.right - off);
-        end = min(tq, key + m.left - off + 1);
-    }
-    first = max(first, 0);
-    end = min(end, tq);
-    if (end < first) end = first;
 }
 
 // Offsets of packed sequences kept in shared memory (dkdv); the fused form, whose tiles fill shared
@@ -232,6 +160,19 @@ __global__ void __launch_bounds__(PLAN_THREADS) bwd_plan_kernel(const Sm100BwdAr
         for (int j = f; j < f + n; ++j) ahead += (work[j] > w) || (work[j] == w && j < i);
         for (int hk = 0; hk < a.hkv; ++hk) a.order[before * a.hkv + hk * n + ahead] = i * a.hkv + hk;
     }
+}
+
+// Launches the plan into a.order, or clears a.order when there is nothing to rank or too much to rank
+// in one block (the units then run in index order).
+cudaError_t launch_bwd_plan(Sm100BwdArgs &a, cudaStream_t stream, int *launches) {
+    const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);
+    if (a.order && items > 1 && items <= PLAN_MAX && items * a.hkv <= 0x7fffffffLL / 4) {
+        bwd_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(a, (int)items);
+        *launches += 1;
+        return cudaGetLastError();
+    }
+    a.order = nullptr;
+    return cudaSuccess;
 }
 
 size_t bwd_sm100_order_bytes(int b, int tk, int hkv) {
@@ -1082,13 +1023,7 @@ static cudaError_t launch_t(const Sm100BwdMaps &m, Sm100BwdArgs a, cudaStream_t 
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     const long long items = (long long)a.b * ((a.tk + BIG - 1) / BIG);
-    if (a.order && items > 1 && items <= PLAN_MAX && items * a.hkv <= 0x7fffffffLL / 4) {
-        bwd_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(a, (int)items);
-        *launches += 1;
-        if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    } else {
-        a.order = nullptr;  // too many to rank in one block (or nothing to rank): index order
-    }
+    if ((e = launch_bwd_plan(a, stream, launches)) != cudaSuccess) return e;
     if (items * a.hkv > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     e = fused ? launch_dkdv<T, HD, true>(m, a, items, stream) : launch_dkdv<T, HD, false>(m, a, items, stream);
     *launches += 1;

@@ -436,11 +436,13 @@ cudaError_t read_sm100_status(unsigned int *status, bool clear) {
         e = cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(unsigned int));
         if (e != cudaSuccess) return e;
     }
-    unsigned int bwd = 0, fwd2 = 0;
+    unsigned int bwd = 0, fwd2 = 0, bwd256 = 0;
     e = read_sm100_bwd_status(&bwd, clear);
     if (e != cudaSuccess) return e;
+    e = read_sm100_bwd256_status(&bwd256, clear);
+    if (e != cudaSuccess) return e;
     e = read_sm100_fwd2_status(&fwd2, clear);
-    *status |= bwd | fwd2;
+    *status |= bwd | fwd2 | bwd256;
     return e;
 }
 

@@ -145,15 +145,14 @@ uint64_t sm100_tensor_map_encodes() { return g_map_encodes.load(std::memory_orde
 bool sm100_takes(const dash_attn_params *p, const void *q, const void *k, const void *v, int backward, bool any_size) {
     if (backward && !tma_readable(q, p->do_stride)) return false;  // dO's strides; its base is checked at launch
     if (p->dtype != DASH_ATTN_BF16 && p->dtype != DASH_ATTN_F16) return false;
-    // Head dimension 64 only from 128 queries and 128 keys on: below that there is a single partial
-    // tile of queries or of keys (one block per head), the tensor cores gain nothing, and the generic
-    // kernels' f32 FMA sums keep the log-sum-exp within the one or two units in the last place that
-    // the reference's records allow at those sizes.  (`any_size`, a switch for tests, lifts the size
-    // rule, so that the records themselves can be run through the tensor-core kernels.)
-    // Head dimension 256: the one-tile forward only (two accumulators of 256 columns are all of tensor
-    // memory, so the backward stays on the generic kernels), under the same size rule.
+    // Head dimensions 64 and 256 only from 128 queries and 128 keys on: below that there is a single
+    // partial tile of queries or of keys (one block per head), the tensor cores gain nothing, and the
+    // generic kernels' f32 FMA sums keep the log-sum-exp within the one or two units in the last place
+    // that the reference's records allow at those sizes.  (`any_size`, a switch for tests, lifts the
+    // size rule, so that the records themselves can be run through the tensor-core kernels.)
+    // At 256 the forward is the one-tile kernel and the backward the three passes of bwd256_sm100.cu.
     const bool big = any_size || (p->tq >= 128 && p->tk >= 128);
-    if (p->d != 128 && !(p->d == 64 && big) && !(p->d == 256 && big && !backward)) return false;
+    if (p->d != 128 && !((p->d == 64 || p->d == 256) && big)) return false;
     const float scale = resolved_scale(p);
     if (!(scale > 0.f) || !std::isfinite(scale)) return false;  // the row maximum is taken before scaling
     if (!q || !k || !v) return false;
@@ -234,6 +233,7 @@ cudaError_t sm100_backward(const dash_attn_params *p, const TrainArgs &a, void *
     f.mask = a.mask;
     f.order = static_cast<int *>(workspace);
     f.dq_acc = dq_acc;
+    if (p->d == 256) return launch_bwd256_sm100(p->dtype, m, f, stream, launches);
     return launch_bwd_sm100(p->dtype, m, f, stream, launches);
 }
 

@@ -41,6 +41,10 @@ struct Sm100BwdMaps {
 // Adds the kernels it launched to *launches.
 cudaError_t launch_bwd_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream, int *launches);
 size_t bwd_sm100_order_bytes(int b, int tk, int hkv);
+cudaError_t launch_bwd_plan(Sm100BwdArgs &a, cudaStream_t stream, int *launches);
+// Head dimension 256: the dq pass, the plan, and the dk and dv passes as one launch (bwd256_sm100.cu).
+cudaError_t launch_bwd256_sm100(int dtype, const Sm100BwdMaps &m, const Sm100BwdArgs &a, cudaStream_t stream, int *launches);
+cudaError_t read_sm100_bwd256_status(unsigned int *status, bool clear);
 size_t bwd_sm100_fused_shared_bytes(int d);
 
 cudaError_t launch_fwd_sm100(int dtype, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,

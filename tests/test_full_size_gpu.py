@@ -15,8 +15,9 @@ from oracle import attention_oracle as oracle
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 # bf16 results against the f64 oracle: o, lse, dq, dk, dv relative to each part's largest value
-# (the bounds of test_kernels_gpu.OWN: one rounding of the dtype plus the rounded P / dS).
-TOL = [5.0e-3, 1e-6, 8.0e-3, 5.5e-3, 5.0e-3]
+# (the bounds of test_kernels_gpu.OWN: one rounding of the dtype plus the rounded P / dS; measured on
+# the sequences checked below: 2.7e-3, 1.3e-7, 3.8e-3, 3.4e-3, 3.1e-3).
+TOL = [4.2e-3, 4.4e-7, 7.7e-3, 4.6e-3, 5.0e-3]
 # A single sampled query is normalised by the largest value of its own row only, which sits well
 # under the tensor's: P rounded to bf16 (2^-9 of sum p|v| / l, up to twice the row's largest output
 # over ~100 keys) plus the output's own rounding (2^-9).

@@ -33,10 +33,10 @@ DECODE = {DType.BF16: 2.2e-3, DType.F16: 2.6e-4, DType.F32: 2e-6}
 # (3.9e-3 in bf16, 4.9e-4 in f16), depending on where that value sits between two powers of two, so a
 # bound of 3.3e-3 is a property of the reference's shapes and seeds.  Largest errors measured on the
 # 54 cases below (D = 128, 64, 256; bf16 | f16): o 4.01e-3 | 4.77e-4, lse 2.2e-7, dq 4.78e-3 | 5.96e-4,
-# dk 4.08e-3 | 6.04e-4, dv 4.26e-3 | 4.63e-4.
+# dk 4.08e-3 | 6.04e-4, dv 4.71e-3 | 5.15e-4 (both maxima on the D = 256 backward, whose dV sums P rounded to the input dtype over 256-wide rows).
 OWN = {
-    DType.BF16: [4.2e-3, 4.4e-7, 7.7e-3, 4.6e-3, 4.4e-3],
-    DType.F16: [5.0e-4, 4.4e-7, 7.3e-4, 6.8e-4, 4.9e-4],
+    DType.BF16: [4.2e-3, 4.4e-7, 7.7e-3, 4.6e-3, 5.0e-3],
+    DType.F16: [5.0e-4, 4.4e-7, 7.3e-4, 6.8e-4, 5.5e-4],
     DType.F32: [1e-5, 1e-6, 1e-5, 1e-5, 1e-5],
 }
 ROUNDING = {DType.BF16: 2.0 ** -8, DType.F16: 2.0 ** -11, DType.F32: 2e-6}
@@ -110,15 +110,17 @@ TC256_CASES = K.tensor_core_cases(256)
 
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=["bf16", "f16"])
 @pytest.mark.parametrize("case", TC256_CASES, ids=[c.name for c in TC256_CASES])
-def test_head_dimension_256_runs_the_tensor_core_forward(adapter, case, dtype):
-    """D = 256 from 128 queries and keys on: the forward on the one-tile tcgen05 kernel (the probe
-    counts it), the backward on the generic kernels, within the bounds of the D = 128 shapes."""
+def test_head_dimension_256_runs_the_tensor_core_kernels(adapter, case, dtype):
+    """D = 256 from 128 queries and keys on: the forward on the one-tile tcgen05 kernel and the backward
+    on the three passes that stream half tiles (the probe counts both), within the bounds of the
+    D = 128 shapes, the same bits on every run."""
     before = _lib.probe("tensor_core_runs")
     got = run_case(adapter, case, dtype)
-    assert _lib.probe("tensor_core_runs") == before + 1, "the forward, and only it, ran on the tensor cores"
+    assert _lib.probe("tensor_core_runs") == before + 2, "the forward and the backward ran on the tensor cores"
     R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
     again = run_case(adapter, case, dtype)
-    assert np.array_equal(got.out, again.out, equal_nan=True) and np.array_equal(got.lse, again.lse)
+    for x, y in zip([got.out, got.lse, *got.grads], [again.out, again.lse, *again.grads]):
+        assert np.array_equal(x, y, equal_nan=True)
 
 
 @pytest.mark.parametrize("case", [TILED_CASES[0], TILED_CASES[10], TC_CASES[6]], ids=["none", "packed", "tc packed"])
