@@ -287,6 +287,7 @@ def main():
     ap.add_argument("--skip-decode", action="store_true", help="leave the decode leg out (profiling captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline out (profiling captures)")
     ap.add_argument("--skip-extra", action="store_true", help="leave the other configurations out (profiling captures)")
+    ap.add_argument("--no-soak", action="store_true", help="leave the half-second soak out (profiling captures)")
     ap.add_argument("--decode-batch", type=int, default=DECODE["b"], help="decode batch (smaller for captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -477,7 +478,7 @@ def main():
     value = total_flops / (step_ms * 1e-3) / 1e12
     # The same step back to back for at least half a second: long enough for the clock sampler to see
     # the GPU under this load, and for the power cap to bite if it is going to.
-    soak_steps = max(args.steps, int(0.6 / (step_ms * 1e-3)) + 1)
+    soak_steps = args.steps if args.no_soak else max(args.steps, int(0.6 / (step_ms * 1e-3)) + 1)
     soak = time_passes(work, soak_steps, 0)
     clocks = sampler.stop() if rank == 0 else None
     soak_leg = {"steps": soak_steps, "ms_per_step": soak["ms_per_step"], "value": total_flops / (soak["ms_per_step"] * 1e-3) / 1e12,

@@ -372,7 +372,7 @@ def test_repeated_calls_reuse_their_tensor_maps(adapter):
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
     def step():
-        rc = lib.dash_attn_forward(ctypes.byref(p), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), None, 0, stream)
+        rc = lib.dash_attn_forward(ctypes.byref(p), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ws.data_ptr(), ws.numel(), stream)
         assert rc == _lib.OK, _lib.last_error()
         rc = lib.dash_attn_backward(ctypes.byref(p), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), g.data_ptr(),
                                     dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(), stream)
@@ -388,7 +388,7 @@ def test_repeated_calls_reuse_their_tensor_maps(adapter):
     torch.cuda.synchronize()
     first_o = o.clone()
     q2 = q.clone()
-    rc = lib.dash_attn_forward(ctypes.byref(p), q2.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), None, 0, stream)
+    rc = lib.dash_attn_forward(ctypes.byref(p), q2.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), ws.data_ptr(), ws.numel(), stream)
     assert rc == _lib.OK and _lib.probe("tensor_map_encodes") - e0 == first + 1, "another query buffer is one new map"
     torch.cuda.synchronize()
     assert torch.equal(o, first_o)
