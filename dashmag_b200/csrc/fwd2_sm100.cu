@@ -6,26 +6,34 @@
 // key-value group over the same rows (grouped heads, even group size), or two consecutive row
 // tiles of one head - so that every K / V tile fetched from L2 feeds twice the arithmetic, and it
 // runs two softmax warpgroups, one per tile, so that every scheduler has two warps of elementwise
-// work to interleave.  352 threads:
+// work to interleave.  384 threads:
 //   warp 0, 10  one lane each issues the TMA tile loads: warp 0 both Q tiles once and then the K
 //               tiles of 128 keys, warp 10 the V tiles, into two-stage rings of 128-byte-swizzled
 //               shared memory;
-//   warp 1      owns tensor memory (512 columns: per tile the 128-column S buffer and the
-//               128-column O accumulator) and issues the tcgen05 MMAs from warp-uniform code under
-//               an elected lane, every one 128 x 128 x 16 (the width at which the tensor cores
-//               run at full rate): O_t += P_t V of the step before, then S_t = Q_t K_j^T, tile by
-//               tile;
+//   warp 1, 11  one lane each issues the tcgen05 MMAs of tile 0 / tile 1 (warp 1 also owns tensor
+//               memory: 512 columns, per tile TWO 64-column S buffers and the 128-column O
+//               accumulator): S_t(u) = Q_t K_u^T (128 x 64 x 16) for sub-steps u of 64 keys into
+//               buffer u & 1, O_t += P_t(u) V_u (128 x 128 x 16, P from tensor memory);
 //   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one query row per thread (TMEM lane =
 //               row): read S from tensor memory, mask what the row does not see, keep the online
 //               softmax in f32 with the scale folded into an exp2, write P rounded to the input
-//               dtype back into tensor memory over the first half of the S columns (two 16-bit
-//               values per 32-bit column: the A operand of P V comes from tensor memory), and at
-//               the end normalise O and store it with the row's log-sum-exp.
-// S is single per tile: S_t of the next step is issued right behind P_t V of this one (MMAs of one
-// thread execute in issue order), and runs - with the other tile's products - under the other
-// tile's softmax.  Lazy row maximum, masking, bounded waits and the status word as in the one-tile
-// kernel (fwd_sm100.cu), which stays for comparison runs.
+//               dtype back into tensor memory over the first half of the columns of the S buffer
+//               it was read from (two 16-bit values per 32-bit column: the A operand of P V comes
+//               from tensor memory), and at the end normalise O and store it with the row's
+//               log-sum-exp.
+// K and V arrive 128 keys at a time; the products and the softmax go through them in two sub-steps
+// of 64 keys, so that a tile has TWO S buffers in the 128 columns one buffer of 128 keys would take.
+// S_t(u + 2) is issued right behind P_t(u) V_u, whose operand it overwrites (MMAs of one thread
+// execute in issue order), which is one sub-step AHEAD of the softmax: when a softmax warp has
+// written P_t(u), S_t(u + 1) is already in the other buffer, and no product sits between two
+// sub-steps of a tile's softmax.  (With one buffer of 128 keys per tile the softmax, P V and the
+// next Q K^T of a tile ran strictly one after another, and that chain, not the tensor cores, set
+// the step.)  Lazy row maximum, masking, bounded waits and the status word as in the one-tile
+// kernel (fwd_sm100.cu).
 #include <cuda.h>
+
+#include <cstddef>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100.h"
@@ -41,7 +49,8 @@ __device__ unsigned int g_sm100_fwd2_status = 0;  // sticky: non-zero once a bou
 namespace {
 
 constexpr int BM = 128;                   // queries per tile
-constexpr int BN = 128;                   // keys per step
+constexpr int BN = 128;                   // keys per K / V tile (one stage of a ring)
+constexpr int SN = 64;                    // keys per sub-step: one S buffer, one pass of the softmax
 constexpr int NT = 2;                     // query tiles per block
 constexpr int NS = 2;                     // stages of the K and of the V ring
 constexpr int HALF_BYTES = 128 * 128;     // 128 rows of 64 features (128 bytes): what one TMA box brings
@@ -54,8 +63,9 @@ template <int HD> struct Geo {
     // 1 KiB slack | Q x 2 | K ring | V ring | Shared
     static constexpr size_t SMEM_BYTES = 1024 + NT * Q_BYTES + 2 * NS * KV_BYTES + 1024;
 };
-constexpr int THREADS = 352;
+constexpr int THREADS = 384;
 constexpr int V_WARP = 10;
+constexpr int MMA_WARP0 = 1, MMA_WARP1 = 11;   // the issuers of tile 0 and of tile 1, on two schedulers
 constexpr float RESCALE_LOG2 = 8.0f;
 // A row that sees at most this many keys keeps the exact running maximum instead of the lazy one:
 // with few keys one of them often carries most of the weight, and only against the exact maximum is
@@ -66,7 +76,9 @@ constexpr int EXACT_KEYS = 512;
 
 struct Barriers {
     uint64_t q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS];
-    uint64_t s_full[NT], p_full[NT][BN / 32], o_ready[NT];   // P arrives 32 keys (two k-steps of P V) at a time
+    uint64_t s_full[NT][2], p_full[NT][2];   // per S buffer
+    uint64_t o_tail[NT], o_done[NT];   // the last P V but one of the tile has completed / the last one has
+    uint64_t turn[4][NT];              // per scheduler: which tile's softmax warp may run its exponentials
 };
 
 struct Shared {
@@ -142,14 +154,18 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(BAR(sh.bar.q_full), 1);
         for (int i = 0; i < NS; ++i) {
             mbar_init(BAR(sh.bar.k_full[i]), 1);
-            mbar_init(BAR(sh.bar.k_empty[i]), 1);
+            mbar_init(BAR(sh.bar.k_empty[i]), NT);   // one commit per tile's issuer
             mbar_init(BAR(sh.bar.v_full[i]), 1);
-            mbar_init(BAR(sh.bar.v_empty[i]), 1);
+            mbar_init(BAR(sh.bar.v_empty[i]), NT);
         }
         for (int t = 0; t < NT; ++t) {
-            mbar_init(BAR(sh.bar.s_full[t]), 1);
-            for (int i = 0; i < BN / 32; ++i) mbar_init(BAR(sh.bar.p_full[t][i]), 4);   // one arrival per softmax warp
-            mbar_init(BAR(sh.bar.o_ready[t]), 1);
+            for (int buf = 0; buf < 2; ++buf) {
+                mbar_init(BAR(sh.bar.s_full[t][buf]), 1);
+                mbar_init(BAR(sh.bar.p_full[t][buf]), 4);   // one arrival per softmax warp
+            }
+            mbar_init(BAR(sh.bar.o_tail[t]), 1);
+            mbar_init(BAR(sh.bar.o_done[t]), 1);
+            for (int w = 0; w < 4; ++w) mbar_init(BAR(sh.bar.turn[w][t]), 1);
         }
         fence_mbar_init();
         prefetch_tensormap(&tm_q);
@@ -193,10 +209,11 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
     for (int i = 0; i < 4 * NT; ++i) { kmin = min(kmin, sh.red_lo[i]); kmax = max(kmax, sh.red_hi[i]); }
     const bool aborted = sh.abort != 0;
-    const int steps = (!aborted && kmax > kmin) ? (kmax - kmin + BN - 1) / BN : 0;
+    const int subs = (!aborted && kmax > kmin) ? (kmax - kmin + SN - 1) / SN : 0;   // sub-steps of 64 keys
+    const int steps = (subs + 1) / 2;                                                // K / V tiles of 128 keys
     bool failed = aborted;
-    // TMEM columns: S[tile] at 128 tile (P over its first 64 columns), O[tile] at 256 + 128 tile.
-    auto COL_S = [](int t) { return static_cast<uint32_t>(t * BN); };
+    // TMEM columns: S[tile][buffer] at 128 tile + 64 buffer (P over its first 32 columns), O[tile] at 256 + HD tile.
+    auto COL_S = [](int t, int buf) { return static_cast<uint32_t>(t * BN + buf * SN); };
     auto COL_O = [](int t) { return static_cast<uint32_t>(256 + t * HD); };
 
     if (warp == 0) {
@@ -223,66 +240,95 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 for (int half = 0; half < HALVES; ++half) tma_load_4d(dst + half * KV_HALF, &tm_v, full, 64 * half, hk, k0, b);
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
-        if (steps > 0) {
-            constexpr uint32_t IDESC_S = idesc_f16(BM, BN, Pack<T>::FMT, 0, 0);   // [128 q x 128 keys], A = Q, B = K K-major
-            constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // [128 q x 128 d], A = P (TMEM), B = V MN-major
-            uint64_t q_desc[NT];
+    } else if (warp == MMA_WARP0 || warp == MMA_WARP1) {
+        // ---------------- MMA issuers: one thread per tile ----------------
+        // The tensor pipe takes MMAs from a short queue: whatever the issuing thread does between two of
+        // them - an election, a warp vote, a poll of a barrier - is time the pipe stands still unless
+        // another thread's MMAs fill it.  So each tile has an issuing thread of its own, on a scheduler
+        // of its own, whose waits fall under the other tile's products, and the thread runs straight-line
+        // code: no election, no votes, descriptors made by additions.
+        if (lane == 0 && subs > 0) {
+            const int t = warp == MMA_WARP0 ? 0 : 1;
+            constexpr uint32_t IDESC_S = idesc_f16(BM, SN, Pack<T>::FMT, 0, 0);   // [128 q x 64 keys], A = Q, B = K K-major
+            constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // [128 q x HD], A = P (TMEM), B = V MN-major
+            // What follows is written for the issuing thread's instruction count, not for looks: one thread
+            // runs dependent instructions at one per four or five cycles, so a hundred instructions between
+            // two runs of MMAs are five hundred cycles in which the tensor pipe, whose queue is short, drains.
+            // Every address is a register plus a constant: barriers from one base, descriptors as a shared
+            // high word and a low word (the address field) per operand, and the loop is unrolled four times
+            // so that the stage and the half of a sub-step are constants.
+            const uint64_t qk_desc = smem_desc_sw128(smem_u32(q_s + t * Q_BYTES), 16, 1024);
+            // V rows are keys (the K of this product): 64-column halves KV_HALF apart, 8-key groups 1024 B apart.
+            const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s), KV_HALF, 1024);
+            const uint32_t q_lo = static_cast<uint32_t>(qk_desc), qk_hi = static_cast<uint32_t>(qk_desc >> 32);
+            const uint32_t k_lo = static_cast<uint32_t>(smem_desc_sw128(smem_u32(k_s), 16, 1024));
+            const uint32_t v_lo = static_cast<uint32_t>(v_desc), v_hi = static_cast<uint32_t>(v_desc >> 32);
+            const uint32_t col_s = tmem + COL_S(t, 0), col_o = tmem + COL_O(t);
+            const uint32_t bars = BAR(sh.bar.q_full);
+            auto bar_at = [&](size_t offset) { return bars + static_cast<uint32_t>(offset); };
+#define FWD2_BAR(member) bar_at(offsetof(Barriers, member))
+            // Keys 64 half .. of stage st: 64 rows of 128 bytes further down in each 64-feature half of the tile.
+            auto tile_at = [](int st, int half) { return static_cast<uint32_t>((st * KV_BYTES + half * SN * 128) >> 4); };
+            // S_t = Q_t K^T for the 64 keys of (st, half), into S buffer `half`
+            auto qk = [&](int st, int half) {
 #pragma unroll
-            for (int t = 0; t < NT; ++t) q_desc[t] = smem_desc_sw128(smem_u32(q_s + t * Q_BYTES), 16, 1024);
-            // S_t(j) = Q_t K_j^T; the K stage is released behind the second tile's.
-            auto issue_s = [&](int j, int t) -> bool {
-                const int st = j % NS, kph = (j / NS) & 1;
-                if (t == 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.k_full[st]), kph))) return false;
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    umma_f16_words(col_s + half * SN, q_lo + (((ks >> 2) * Q_HALF + (ks & 3) * 32) >> 4), qk_hi,
+                                   k_lo + tile_at(st, half) + (((ks >> 2) * KV_HALF + (ks & 3) * 32) >> 4), qk_hi, IDESC_S, ks > 0 ? 1u : 0u);
+            };
+            // Sub-step u = 4 i + R: stage R / 2, half R % 2 - one uninterrupted run of MMAs (P V of the sub-step
+            // and S of the next but one, which overwrites its operand, behind it), every wait before the run and
+            // every commit after it.  Parities: P / S buffers are reused every second sub-step, stages every fourth.
+            auto sub_step = [&](auto r_, int i, int u) -> bool {
+                constexpr int R = decltype(r_)::value, st = R >> 1, half = R & 1;
+                const bool more = u + 2 < subs;
+                if (half == 0) {
+                    if (!mbar_wait(FWD2_BAR(v_full) + 8 * st, i & 1)) return false;
+                    if (more && !mbar_wait(FWD2_BAR(k_full) + 8 * (st ^ 1), (i + st) & 1)) return false;
+                }
+                if (!mbar_wait(FWD2_BAR(p_full) + 8 * (2 * t + half), st)) return false;
                 tc_fence_after_sync();
-                const uint64_t k_desc = smem_desc_sw128(smem_u32(k_s + st * KV_BYTES), 16, 1024);
-                const uint32_t sf = BAR(sh.bar.s_full[t]), ke = BAR(sh.bar.k_empty[st]);
-                if (elect_one()) {
 #pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks)
-                        umma_f16(tmem + COL_S(t), desc_at(q_desc[t], (ks >> 2) * Q_HALF + (ks & 3) * 32),
-                                 desc_at(k_desc, (ks >> 2) * KV_HALF + (ks & 3) * 32), IDESC_S, ks > 0 ? 1u : 0u);
-                    umma_commit(sf);
-                    if (t == NT - 1) umma_commit(ke);
+                for (int ks = 0; ks < SN / 16; ++ks)
+                    umma_f16_ts_words(col_o, col_s + half * SN + ks * 8, v_lo + tile_at(st, half) + ((ks * 2048) >> 4), v_hi, IDESC_O,
+                                      (u > 0 || ks > 0) ? 1u : 0u);
+                if (more) {
+                    qk(st ^ 1, half);
+                    umma_commit(FWD2_BAR(s_full) + 8 * (2 * t + half));
+                    // both issuers release a stage: behind the product on its second half, or on the last sub-step
+                    if (half == 1 || u + 2 == subs - 1) umma_commit(FWD2_BAR(k_empty) + 8 * (st ^ 1));
                 }
-                __syncwarp();
+                // No commit per product for O: a row that has to rescale O (rare) learns that P V of u - 1
+                // has completed from S of u + 1, which is issued behind it - or, at the last sub-step, from
+                // o_tail; the epilogue waits for o_done.
+                if (u >= subs - 2) umma_commit(u == subs - 1 ? FWD2_BAR(o_done) + 8 * t : FWD2_BAR(o_tail) + 8 * t);
+                if (half == 1 || u == subs - 1) umma_commit(FWD2_BAR(v_empty) + 8 * st);
                 return true;
             };
-            // O_t += P_t(i) V_i with P read from the S columns of the tile; the V stage is released
-            // behind the second tile's.
-            auto issue_pv = [&](int i, int t) -> bool {
-                const int st = i % NS, vph = (i / NS) & 1;
-                if (t == 0 && !__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.v_full[st]), vph))) return false;
-                // V rows are keys (the K of this product): 64-column halves KV_HALF apart, 8-key groups 1024 B apart.
-                const uint64_t v_desc = smem_desc_sw128(smem_u32(v_s + st * KV_BYTES), KV_HALF, 1024);
-                const uint32_t orr = BAR(sh.bar.o_ready[t]), ve = BAR(sh.bar.v_empty[st]);
-#pragma unroll
-                for (int part = 0; part < BN / 32; ++part) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.p_full[t][part]), i & 1))) return false;
-                    tc_fence_after_sync();
-                    if (elect_one()) {
-#pragma unroll
-                        for (int ks = 2 * part; ks < 2 * part + 2; ++ks)
-                            umma_f16_ts(tmem + COL_O(t), tmem + COL_S(t) + ks * 8, desc_at(v_desc, ks * 2048), IDESC_O,
-                                        (i > 0 || ks > 0) ? 1u : 0u);
-                        if (part == BN / 32 - 1) {
-                            umma_commit(orr);
-                            if (t == NT - 1) umma_commit(ve);
-                        }
-                    }
-                    __syncwarp();
+            // Two sub-steps of S ahead ...
+            if (!(mbar_wait(FWD2_BAR(q_full), 0) && mbar_wait(FWD2_BAR(k_full), 0))) failed = true;
+            if (!failed) {
+                tc_fence_after_sync();
+                qk(0, 0);
+                umma_commit(FWD2_BAR(s_full) + 8 * (2 * t));
+                if (subs > 1) {
+                    qk(0, 1);
+                    umma_commit(FWD2_BAR(s_full) + 8 * (2 * t + 1));
                 }
-                return true;
-            };
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.q_full), 0))) failed = true;
-            if (!failed && !(issue_s(0, 0) && issue_s(0, 1))) failed = true;
-            for (int j = 1; j < steps && !failed; ++j) {
-#pragma unroll
-                for (int t = 0; t < NT; ++t)
-                    if (!(issue_pv(j - 1, t) && issue_s(j, t))) { failed = true; break; }
+                umma_commit(FWD2_BAR(k_empty));
+                // ... then the sub-steps, four to a round of the two stages.
+#pragma unroll 1
+                for (int i = 0, u = 0; u < subs; ++i, u += 4) {
+                    if (!sub_step(std::integral_constant<int, 0>{}, i, u)) { failed = true; break; }
+                    if (u + 1 >= subs) break;
+                    if (!sub_step(std::integral_constant<int, 1>{}, i, u + 1)) { failed = true; break; }
+                    if (u + 2 >= subs) break;
+                    if (!sub_step(std::integral_constant<int, 2>{}, i, u + 2)) { failed = true; break; }
+                    if (u + 3 >= subs) break;
+                    if (!sub_step(std::integral_constant<int, 3>{}, i, u + 3)) { failed = true; break; }
+                }
             }
-            if (!failed && !(issue_pv(steps - 1, 0) && issue_pv(steps - 1, 1))) failed = true;
+#undef FWD2_BAR
         }
     } else {
         // ---------------- softmax of one tile, one row per thread ----------------
@@ -293,27 +339,27 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const float2 sl2 = make_float2(a.scale_log2, a.scale_log2);
         float m_ref = -INFINITY, l = 0.f;
         const float rescale_at = hi - lo <= EXACT_KEYS ? 0.f : RESCALE_LOG2;
-        for (int j = 0; j < steps && !failed; ++j) {
-            const int k0 = kmin + j * BN;
-            uint32_t pb[BN / 32] = {0, 0, 0, 0};
+        for (int u = 0; u < subs && !failed; ++u) {
+            const int k0 = kmin + u * SN, buf = u & 1;
+            uint32_t pb[SN / 32] = {0, 0};
             if (padded) {
 #pragma unroll
-                for (int i = 0; i < BN / 32; ++i) {
+                for (int i = 0; i < SN / 32; ++i) {
                     const int key = k0 + i * 32 + lane;
                     pb[i] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
                 }
             }
-            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full[t]), j & 1))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full[t][buf]), (u >> 1) & 1))) { failed = true; break; }
             tc_fence_after_sync();
-            float s[BN];
+            float s[SN];
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) tmem_ld32(t_lane + COL_S(t) + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+            for (int c = 0; c < SN / 32; ++c) tmem_ld32(t_lane + COL_S(t, buf) + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
             tmem_ld_wait();
 
-            const bool clear = !padded && k0 >= lo && k0 + BN <= hi;  // the row sees the whole step
+            const bool clear = !padded && k0 >= lo && k0 + SN <= hi;  // the row sees the whole sub-step
             if (!__all_sync(0xffffffffu, clear)) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
+                for (int c = 0; c < SN; ++c) {
                     const int key = k0 + c;
                     const bool vis = key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u);
                     s[c] = vis ? s[c] : -INFINITY;
@@ -324,10 +370,10 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
             for (int e = 0; e < 8; ++e) mx8[e] = fmax3(s[e], s[8 + e], s[16 + e]);
 #pragma unroll
-            for (int c = 24; c < BN; c += 16)
+            for (int c = 24; c < SN; c += 16)
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
-                    mx8[e] = c + 8 + e < BN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
+                    mx8[e] = c + 8 + e < SN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
             const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
             // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8 - or by
             // anything at all, for a row of few keys (see EXACT_KEYS).
@@ -346,48 +392,68 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float neg = m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
             const float2 neg2 = make_float2(neg, neg);
 
-            // O holds steps 0..j-1 once P V of step j - 1 has completed (it has: S of this step was
-            // issued behind it); rescale it before any of P V of step j is issued.
-            if (j > 0) {
-                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (j - 1) & 1))) { failed = true; break; }
-                if (__any_sync(0xffffffffu, rescale)) rescale_accumulator<HD>(t_lane + COL_O(t), factor);
+            // Only a moved reference touches O, and it has to see sub-steps 0..u-1 in it.  P V of u - 2 has
+            // completed (S of this sub-step was issued behind it); P V of u - 1 - whose P this warp arrived a
+            // moment ago - may not have.  S of u + 1 is issued behind it, so the warp waits for that (the
+            // barrier it waits on at the next sub-step anyway: of its phases, that of S(u - 1) has completed
+            // and that of S(u + 3) cannot have), or for o_tail at the last sub-step.
+            if (u > 0 && __any_sync(0xffffffffu, rescale)) {
+                const bool ok = u + 1 < subs ? mbar_wait(BAR(sh.bar.s_full[t][buf ^ 1]), ((u + 1) >> 1) & 1)
+                                             : mbar_wait(BAR(sh.bar.o_tail[t]), 0);
+                if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
+                rescale_accumulator<HD>(t_lane + COL_O(t), factor);
             }
-            // P over the first 64 of the S columns this thread has read, 32 keys (16 columns, two
-            // k-steps of P V) at a time: the tensor cores start on a part while the next is made.
+            // The special-function pipe takes one warp instruction in eight cycles: the 64 exponentials of a
+            // warp are 512 cycles of it, and the two softmax warps of a scheduler - one per tile - that run
+            // them at the same time each take twice that, after which the pipe stands idle while both do the
+            // rest of their sub-steps.  So the two take turns: tile 0's warp runs the exponentials of sub-step
+            // u, then tile 1's, then tile 0's of u + 1 ..., each doing the rest of its sub-step (the wait for
+            // S, the maximum, the store of P) under the other's turn.  (Bounded waits on barriers of the
+            // block's own, like every other wait here; both tiles sweep the same sub-steps.)
+            if (t == 1 || u > 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.turn[warp & 3][t]), (t == 1 ? u : u - 1) & 1))) { failed = true; break; }
+            }
+            // P over the first 32 columns of the buffer this thread has read (two 16-bit values a column).
             float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int cc = 0; cc < BN / 32; ++cc) {
+            for (int cc = 0; cc < SN / 32; ++cc) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
+#if defined(FWD2_NO_EXP)
+                    const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
+                    const float p0 = x.x * 0.001f, p1 = x.y * 0.001f;
+#else
                     const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
                     const float p0 = ex2(x.x), p1 = ex2(x.y);
+#endif
                     sum2[e & 3] = add2(sum2[e & 3], make_float2(p0, p1));
                     pk[e] = Pack<T>::two(p0, p1);
                 }
-                tmem_st16(t_lane + COL_S(t) + cc * 16, pk);
-                tmem_st_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[t][cc]));
+                tmem_st16(t_lane + COL_S(t, buf) + cc * 16, pk);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.turn[warp & 3][t ^ 1]));   // the other tile's turn
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[t][buf]));
             {
                 const float2 tsum = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
                 l += tsum.x + tsum.y;
             }
         }
-
         // ---------------- epilogue ----------------
         T *out = static_cast<T *>(a.out);
         const int64_t base = ((int64_t)b * a.tq + row) * a.hq + h;
-        if (steps == 0 || failed) {
+        if (subs == 0 || failed) {
             if (row < a.tq && !failed) {
                 const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (int c = 0; c < HD / 8; ++c) reinterpret_cast<uint4 *>(out + base * HD)[c] = z;
                 a.lse[base] = -INFINITY;
             }
-        } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_ready[t]), (steps - 1) & 1))) {
+        } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.o_done[t]), 0))) {
             // Every MMA has completed, so the tile's Q is dead: the normalised rows are staged over
             // it in the layout of the TMA box (two halves of 64 columns, 128-byte rows, 16-byte
             // chunks XOR-swizzled by the row) and leave as two bulk stores - whole lines instead of

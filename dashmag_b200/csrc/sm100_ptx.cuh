@@ -43,8 +43,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Waits for the phase of `parity` to complete, but never forever: after about a second of polling
 // (2^31 cycles of this multiprocessor's clock) it gives up and returns false, so that a broken
 // pipeline ends in an error status instead of a hung GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
     const long long start = clock64();
     for (;;) {
         // The clock is read once per 64 polls: reading it competes with the exponentials for
@@ -54,6 +53,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
             if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - start > (1LL << 31)) return false;
     }
+}
+// (The polling loop is out of line: the fast path - the phase has completed already - is two
+// instructions in the caller, which matters to a thread that feeds the tensor pipe.)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity);
 }
 
 // One lane of the (converged) warp, the same one every time it is asked.  The MMA-issuing warp
@@ -198,6 +203,36 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
         "}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same two with each 64-bit descriptor given as its two words: of a tile's descriptors only the
+// low word (the address) differs, so a thread that issues many MMAs keeps ONE high word per operand
+// layout and forms every descriptor by one 32-bit addition.
+__device__ __forceinline__ void umma_f16_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                  uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // The mbarrier gets one arrival when every MMA this thread has issued so far has completed.
