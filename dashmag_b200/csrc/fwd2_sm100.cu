@@ -28,8 +28,9 @@
 // written P_t(u), S_t(u + 1) is already in the other buffer, and no product sits between two
 // sub-steps of a tile's softmax.  (With one buffer of 128 keys per tile the softmax, P V and the
 // next Q K^T of a tile ran strictly one after another, and that chain, not the tensor cores, set
-// the step.)  Lazy row maximum, masking, bounded waits and the status word as in the one-tile
-// kernel (fwd_sm100.cu).
+// the step.)  The two softmax warps of a scheduler - one per tile - take turns at their exponentials,
+// which the special-function pipe would otherwise run at half speed for both, and idle after.  Lazy
+// row maximum, masking, bounded waits and the status word as in the one-tile kernel (fwd_sm100.cu).
 #include <cuda.h>
 
 #include <cstddef>
@@ -241,19 +242,16 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
     } else if (warp == MMA_WARP0 || warp == MMA_WARP1) {
-        // ---------------- MMA issuers: one thread per tile ----------------
-        // The tensor pipe takes MMAs from a short queue: whatever the issuing thread does between two of
-        // them - an election, a warp vote, a poll of a barrier - is time the pipe stands still unless
-        // another thread's MMAs fill it.  So each tile has an issuing thread of its own, on a scheduler
-        // of its own, whose waits fall under the other tile's products, and the thread runs straight-line
-        // code: no election, no votes, descriptors made by additions.
-        if (lane == 0 && subs > 0) {
-            const int t = warp == MMA_WARP0 ? 0 : 1;
+        // ---------------- MMA issuers: one warp per tile, one elected lane issuing ----------------
+        // The tensor pipe takes MMAs from a short queue: whatever the issuer does between two of them - a
+        // poll of a barrier, address arithmetic - is time the pipe stands still unless another issuer's MMAs
+        // fill it.  So each tile has an issuing warp of its own, on a scheduler of its own, whose waits fall
+        // under the other tile's products.  The whole warp runs the (warp-uniform) code, so that barrier
+        // addresses and descriptors are made in the uniform datapath; one elected lane issues.
+        if (subs > 0) {
+            const int t = __shfl_sync(0xffffffffu, warp, 0) == MMA_WARP0 ? 0 : 1;
             constexpr uint32_t IDESC_S = idesc_f16(BM, SN, Pack<T>::FMT, 0, 0);   // [128 q x 64 keys], A = Q, B = K K-major
             constexpr uint32_t IDESC_O = idesc_f16(BM, HD, Pack<T>::FMT, 0, 1);   // [128 q x HD], A = P (TMEM), B = V MN-major
-            // What follows is written for the issuing thread's instruction count, not for looks: one thread
-            // runs dependent instructions at one per four or five cycles, so a hundred instructions between
-            // two runs of MMAs are five hundred cycles in which the tensor pipe, whose queue is short, drains.
             // Every address is a register plus a constant: barriers from one base, descriptors as a shared
             // high word and a low word (the address field) per operand, and the loop is unrolled four times
             // so that the stage and the half of a sub-step are constants.
@@ -288,6 +286,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 if (!mbar_wait(FWD2_BAR(p_full) + 8 * (2 * t + half), st)) return false;
                 tc_fence_after_sync();
+                if (elect_one()) {
 #pragma unroll
                 for (int ks = 0; ks < SN / 16; ++ks)
                     umma_f16_ts_words(col_o, col_s + half * SN + ks * 8, v_lo + tile_at(st, half) + ((ks * 2048) >> 4), v_hi, IDESC_O,
@@ -303,12 +302,14 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // o_tail; the epilogue waits for o_done.
                 if (u >= subs - 2) umma_commit(u == subs - 1 ? FWD2_BAR(o_done) + 8 * t : FWD2_BAR(o_tail) + 8 * t);
                 if (half == 1 || u == subs - 1) umma_commit(FWD2_BAR(v_empty) + 8 * st);
+                }
                 return true;
             };
             // Two sub-steps of S ahead ...
             if (!(mbar_wait(FWD2_BAR(q_full), 0) && mbar_wait(FWD2_BAR(k_full), 0))) failed = true;
             if (!failed) {
                 tc_fence_after_sync();
+                if (elect_one()) {
                 qk(0, 0);
                 umma_commit(FWD2_BAR(s_full) + 8 * (2 * t));
                 if (subs > 1) {
@@ -316,6 +317,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     umma_commit(FWD2_BAR(s_full) + 8 * (2 * t + 1));
                 }
                 umma_commit(FWD2_BAR(k_empty));
+                }
                 // ... then the sub-steps, four to a round of the two stages.
 #pragma unroll 1
                 for (int i = 0, u = 0; u < subs; ++i, u += 4) {
@@ -420,13 +422,8 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-#if defined(FWD2_NO_EXP)
-                    const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
-                    const float p0 = x.x * 0.001f, p1 = x.y * 0.001f;
-#else
                     const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
                     const float p0 = ex2(x.x), p1 = ex2(x.y);
-#endif
                     sum2[e & 3] = add2(sum2[e & 3], make_float2(p0, p1));
                     pk[e] = Pack<T>::two(p0, p1);
                 }
