@@ -61,9 +61,12 @@ constexpr float LOG2E = 1.4426950408889634f;
 // 2^x on the special-function pipe or, for a share of the elements, on the FMA pipe.
 template <bool POLY> __device__ __forceinline__ float exp2_mixed(float x) { return POLY ? ex2_poly3(x) : ex2(x); }
 
-// Of every four exponentials, how many run on the FMA pipe (ex2_poly3): one for bf16, whose rounding step
-// (2^-9) is thirty times the cubic's error; none for f16, whose step (2^-12) is only four times it.
+// Of every four exponentials, how many run on the FMA pipe (ex2_poly3).  dkdv: one for bf16, whose rounding
+// step (2^-9) is thirty times the cubic's error; none for f16, whose step (2^-12) is only four times it.  dq:
+// none - its elementwise warps are not held up by the special-function pipe, and every cubic is ten
+// instructions for one (measured on config 2: 35 us of 1 370 slower with a quarter as cubics).
 template <typename T> constexpr int poly_of4() { return Pack<T>::FMT == 1 ? 1 : 0; }
+template <typename T> constexpr int poly_of4_dq() { return 0; }
 
 // `groups` x 32 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as
 // contiguous elements of the row.
@@ -904,10 +907,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             }
 #pragma unroll
             for (int c4 = 0; c4 < KQW / 4; ++c4) {
-                p[c4 * 4 + 0] = exp2_mixed<(poly_of4<T>() > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2));
-                p[c4 * 4 + 1] = exp2_mixed<(poly_of4<T>() > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2));
-                p[c4 * 4 + 2] = exp2_mixed<(poly_of4<T>() > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2));
-                p[c4 * 4 + 3] = exp2_mixed<(poly_of4<T>() > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2));
+                p[c4 * 4 + 0] = exp2_mixed<(poly_of4_dq<T>() > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2));
+                p[c4 * 4 + 1] = exp2_mixed<(poly_of4_dq<T>() > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2));
+                p[c4 * 4 + 2] = exp2_mixed<(poly_of4_dq<T>() > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2));
+                p[c4 * 4 + 3] = exp2_mixed<(poly_of4_dq<T>() > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2));
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full[st]), (t >> 1) & 1))) { failed = true; break; }
             tc_fence_after_sync();
