@@ -66,13 +66,15 @@ def test_the_ranks_shares_put_together_are_the_whole_call(world, hkv, window):
         else:
             got, want = got.float(), want.float()
             # o: its own rounding (neighbouring bf16 values) plus P rounded against other step boundaries (2^-9 of
-            # each weight); lse: f32 rounding; the gradients: two roundings of P / dS apart
+            # each weight); lse: f32 rounding; the gradients: both results lie within the parity bound of the exact
+            # gradient (dQ 7.7e-3, dK 4.6e-3, dV 5.0e-3 of the largest value, tests/test_full_size_gpu.py), so they
+            # lie within twice that of each other
             if name == "o":
                 bound = 2.0 ** -7 * want.abs() + 1e-3 * float(want.abs().max())
             elif name == "lse":
                 bound = 1e-6 * want.abs().clamp_min(1.0)
             else:
-                bound = torch.full_like(want, 4e-3 * float(want.abs().max()))
+                bound = torch.full_like(want, 2 * {"dq": 7.7e-3, "dk": 4.6e-3, "dv": 5.0e-3}[name] * float(want.abs().max()))
             finite = torch.isfinite(want)
             assert torch.equal(torch.isfinite(got), finite), name
             assert bool(((got - want).abs()[finite] <= bound[finite]).all()), f"{name}: a bin of sequences differs from the whole call"
