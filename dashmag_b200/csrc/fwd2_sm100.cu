@@ -419,18 +419,28 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
             for (int cc = 0; cc < SN / 32; ++cc) {
-                uint32_t pk[16];
+                float pe[32];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
-                    const float p0 = ex2(x.x), p1 = ex2(x.y);
-                    sum2[e & 3] = add2(sum2[e & 3], make_float2(p0, p1));
-                    pk[e] = Pack<T>::two(p0, p1);
+                    pe[2 * e] = ex2_ordered(x.x);
+                    pe[2 * e + 1] = ex2_ordered(x.y);
+                }
+                if (cc == SN / 32 - 1) {
+                    // The last exponential of the sub-step has been issued: the other tile's turn.  (Handed over
+                    // here, not behind the packing and the store of P, which need no special-function pipe - the
+                    // exponentials are volatile asm so that the compiler keeps them in front of the arrival.)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(sh.bar.turn[warp & 3][t ^ 1]));
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    sum2[e & 3] = add2(sum2[e & 3], make_float2(pe[2 * e], pe[2 * e + 1]));
+                    pk[e] = Pack<T>::two(pe[2 * e], pe[2 * e + 1]);
                 }
                 tmem_st16(t_lane + COL_S(t, buf) + cc * 16, pk);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(BAR(sh.bar.turn[warp & 3][t ^ 1]));   // the other tile's turn
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
