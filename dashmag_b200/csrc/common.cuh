@@ -106,6 +106,36 @@ __device__ __forceinline__ void row_bounds(const MaskArgs &m, int row, int tq, i
     }
 }
 
+// The same for the 32 rows of a (converged) warp at once.  A thread that places its row by itself walks
+// the packed offsets by bisection - three or four DEPENDENT loads from global memory, some two thousand
+// cycles of a block's set-up before its first tile load can be issued.  Here each lane fetches ONE pair of
+// offsets (lane i: cu_q[i], cu_k[i]; batches of up to 31 sequences, else every lane falls back to
+// row_bounds), the rows are placed by comparing against the lanes' values, and the four offsets of a row's
+// sequence come by shuffle: one load latency instead of four.  All 32 lanes must call; results are
+// identical to row_bounds.
+__device__ __forceinline__ void row_bounds_warp(const MaskArgs &m, int row, int tq, int tk, int &lo, int &hi) {
+    if (m.kind != 2 || m.seqs > 31) {
+        row_bounds(m, row, tq, tk, lo, hi);
+        return;
+    }
+    const int lane = threadIdx.x & 31;
+    const int cq = lane <= m.seqs ? load_index(m.cu_q, m.idx_bytes, lane) : 2147483647;
+    const int ck = lane <= m.seqs ? load_index(m.cu_k, m.idx_bytes, lane) : 2147483647;
+    int s = -1;   // the last s with cu_q[s] <= row: the offsets do not decrease, so it is a count
+    for (int i = 0; i <= m.seqs; ++i) s += __shfl_sync(0xffffffffu, cq, i) <= row ? 1 : 0;
+    const int sc = min(max(s, 0), 30);
+    const int q0 = __shfl_sync(0xffffffffu, cq, sc), q1 = __shfl_sync(0xffffffffu, cq, sc + 1);
+    const int k0 = __shfl_sync(0xffffffffu, ck, sc), k1 = __shfl_sync(0xffffffffu, ck, sc + 1);
+    lo = tk;
+    hi = 0;
+    if (row < 0 || row >= tq || s < 0 || s >= m.seqs) return;
+    const int lk = k1 - k0, lq = q1 - q0;
+    const int pos = row - q0 + lk - lq;
+    const int a = max(k0 + max(0, pos - m.left), 0);
+    const int c = min(k0 + min(lk, pos + m.right + 1), tk);
+    if (c > a) { lo = a; hi = c; }
+}
+
 __device__ __forceinline__ bool key_padded(const MaskArgs &m, int b, int key) {
     if (m.kind != 1) return false;
     int64_t at = (int64_t)b * m.kp_sb + (int64_t)key * m.kp_st;

@@ -198,7 +198,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int r = lane_base + lane;                // row of the tile
     int lo = a.tk, hi = 0;
     if (warp >= 2 && warp < 2 + 4 * NT) {
-        row_bounds(a.mask, tile_row0(tile) + r, a.tq, a.tk, lo, hi);
+        row_bounds_warp(a.mask, tile_row0(tile) + r, a.tq, a.tk, lo, hi);
         int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
         if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
     }

@@ -144,7 +144,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int r = lane_base + lane;                // row of the tile (softmax threads)
     int lo = a.tk, hi = 0;
     if (warp >= 2 && warp < 6) {
-        row_bounds(a.mask, m0 + r, a.tq, a.tk, lo, hi);
+        row_bounds_warp(a.mask, m0 + r, a.tq, a.tk, lo, hi);
         int wlo = warp_min_i(hi > lo ? lo : a.tk), whi = warp_max_i(hi > lo ? hi : 0);
         if (lane == 0) { sh.red_lo[sw] = wlo; sh.red_hi[sw] = whi; }
     }
