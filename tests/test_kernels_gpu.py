@@ -88,6 +88,44 @@ def test_tensor_core_shapes_match_oracle(adapter, case, dtype, deterministic):
     R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
 
 
+def growing_keys(name, dims, options, seed, step=64):
+    """Keys that double every other block of 64 (powers of two: the values stay representable in the
+    16-bit dtypes), so that a row's largest score moves up by more than the lazy maximum's 2^8 every
+    second sub-step of the forward from the fourth on - the last one included."""
+    case = K.seeded(name, dims, AttentionMask.none(), options, seed)
+    k = case.k.copy()
+    for j in range(0, k.shape[1], step):
+        k[:, j:j + step] *= 2.0 ** ((j // step + 1) // 2)
+    return K.dataclasses.replace(case, k=k)
+
+
+GROWING = [
+    growing_keys("growing keys, 717 of them (an odd count of 64-key sub-steps)", [1, 4, 2, 200, 717, 128], AttentionOptions(), 301),
+    growing_keys("growing keys, causal, 1100", [1, 4, 2, 1100, 1100, 128], AttentionOptions.causal_(), 302),
+    growing_keys("growing keys, D 64, 640", [1, 4, 4, 300, 640, 64], AttentionOptions(), 303),
+]
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", GROWING, ids=[c.name for c in GROWING])
+def test_the_lazy_maximum_moves_again_and_again(adapter, case, dtype):
+    """Rows of more than 512 keys keep the lazy maximum: the accumulator is rescaled through tensor
+    memory whenever the row's largest score outgrew the reference by 2^8, which the forward's softmax
+    warps may only do once the product of the sub-step before has completed - learnt from the S of the
+    NEXT sub-step, or, at the last one, from a barrier of its own.  These keys force that at every kind of
+    sub-step."""
+    before = _lib.probe("tensor_core_runs")
+    got = run_case(adapter, case, dtype)
+    assert _lib.probe("tensor_core_runs") == before + 2
+    # These rows are peaked - one key carries nearly all the weight - and the lazy reference lies up to 2^8
+    # below the row's maximum, so that key's weight, 2^(s - reference), is rounded to the dtype where against
+    # the exact maximum it would be exactly 1: one rounding more than the bounds of the benign shapes hold
+    # (measured here: o 5.0e-3 | 6.2e-4, dk 5.6e-3 | 6.7e-4 of the largest value).  A rescale gone wrong would
+    # be off by factors, not by a rounding; the log-sum-exp keeps its bound.
+    bounds = [1.4 * b if i != 1 else b for i, b in enumerate(OWN[dtype])]
+    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), bounds)
+
+
 TC64_CASES = K.tensor_core_cases(64)
 
 
