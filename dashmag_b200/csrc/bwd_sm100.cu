@@ -49,7 +49,6 @@ template <int HD> constexpr int tile_bytes() { return (HD / 64) * BIG_HALF; }
 constexpr int QS = BIG;                    // rows of a streamed tile: a step
 constexpr int KCG = 4;                     // elementwise warps per TMEM lane quadrant
 constexpr int KQW = QS / KCG;              // columns of a step per elementwise thread
-constexpr int KEW_THREADS = 32 * 4 * KCG;
 constexpr int KAUX_WARP = 2 + 4 * KCG;     // dkdv: one more warp gathers the per-query vectors
 constexpr int KTHREADS = 32 * (3 + 4 * KCG);
 constexpr int KRED_WARP = KAUX_WARP + 1;   // fused dkdv: four more warps (one per TMEM lane quadrant) send dQ out
@@ -66,7 +65,6 @@ template <bool POLY> __device__ __forceinline__ float exp2_mixed(float x) { retu
 // none - its elementwise warps are not held up by the special-function pipe, and every cubic is ten
 // instructions for one (measured on config 2: 35 us of 1 370 slower with a quarter as cubics).
 template <typename T> constexpr int poly_of4() { return Pack<T>::FMT == 1 ? 1 : 0; }
-template <typename T> constexpr int poly_of4_dq() { return 0; }
 
 // `groups` x 32 f32 accumulator columns of this thread's TMEM lane, scaled, rounded and stored as
 // contiguous elements of the row.
@@ -690,6 +688,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 // when dS is written is therefore double as well (one per buffer).
 constexpr int DQ_KS = 3;   // stages of the K ring: a K tile serves S of its step and, a step and a half later, dQ
 
+// dq: two elementwise warps per TMEM lane quadrant, 64 keys of a step per thread (measured on config 2: 573 us
+// against 586 with four warps of 32 keys each; turns at the exponentials, as in the forward, cost 18 us here).
+constexpr int QCG = 2;
+constexpr int QW = BIG / QCG;
+constexpr int QEW_THREADS = 32 * 4 * QCG;
+static_assert(QW % 32 == 0, "whole 32-column TMEM loads per thread");
+
 struct DqBarriers {
     uint64_t res_full;
     uint64_t k_full[DQ_KS], k_empty[DQ_KS], v_full[2], v_empty[2];
@@ -701,7 +706,7 @@ struct DqTail {
     DqBarriers bar;
     uint32_t tmem_base;
     unsigned int abort;
-    int red_lo[4 * KCG], red_hi[4 * KCG];
+    int red_lo[4 * QCG], red_hi[4 * QCG];
     int tile_bad;   // an elementwise warp gave up: dQ of the tile is not stored
 };
 
@@ -709,7 +714,7 @@ constexpr size_t DQ_TAIL = 1024;
 static_assert(sizeof(DqTail) <= DQ_TAIL, "the tail of the dq kernel's shared memory");
 // 1 KiB slack | Q, dO resident (2 x 32 KiB) | K ring 3 x 32 KiB | V ring 2 x 32 KiB | tail
 template <int HD> constexpr size_t smem_dq() { return 1024 + (4 + DQ_KS) * tile_bytes<HD>() + DQ_TAIL; }
-constexpr int DQ_THREADS = 32 * (2 + 4 * KCG);
+constexpr int DQ_THREADS = 32 * (2 + 4 * QCG);
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(DQ_THREADS, 1)
@@ -744,10 +749,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             mbar_init(BAR(sh.bar.v_full[i]), 1);
             mbar_init(BAR(sh.bar.v_empty[i]), 1);
             mbar_init(BAR(sh.bar.dp_full[i]), 1);
-            mbar_init(BAR(sh.bar.ds_full[i]), 4 * KCG);
+            mbar_init(BAR(sh.bar.ds_full[i]), 4 * QCG);
         }
         mbar_init(BAR(sh.bar.s_full), 1);
-        mbar_init(BAR(sh.bar.s_free), 4 * KCG);    // one arrival per elementwise warp
+        mbar_init(BAR(sh.bar.s_free), 4 * QCG);    // one arrival per elementwise warp
         mbar_init(BAR(sh.bar.acc_ready), 1);
         fence_mbar_init();
         prefetch_tensormap(&tm_q);
@@ -869,9 +874,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (!failed && elect_one()) umma_commit(BAR(sh.bar.acc_ready));
         }
     } else {
-        // ---------------- elementwise: a query row and 32 of the step's keys per thread ----------------
+        // ---------------- elementwise: a query row and QW of the step's keys per thread ----------------
         const int row = m0 + r;
-        const int cg = sw >> 2, col0 = cg * KQW;
+        const int cg = sw >> 2, col0 = cg * QW;
         const uint32_t t_lane = tmem + (static_cast<uint32_t>(lane_base) << 16);
         const bool padded = a.mask.kind == 1;
         float l2 = INFINITY, dl = 0.f;
@@ -883,75 +888,88 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         for (int t = 0; t < steps && !failed; ++t) {
             const int st = t & 1, c0 = kmin + t * BIG + col0;
-            uint32_t pb = 0;
-            if (padded) {
-                const int key = c0 + lane;
-                pb = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
+            uint32_t pb[QW / 32];
+#pragma unroll
+            for (int g = 0; g < QW / 32; ++g) {
+                pb[g] = 0;
+                if (padded) {
+                    const int key = c0 + 32 * g + lane;
+                    pb[g] = __ballot_sync(0xffffffffu, key >= a.tk || key_padded(a.mask, b, key));
+                }
             }
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.s_full), t & 1))) { failed = true; break; }
             tc_fence_after_sync();
-            float p[KQW];
-            tmem_ld32(t_lane + COL_S + col0, *reinterpret_cast<uint32_t(*)[32]>(&p[0]));
+            float p[QW];
+#pragma unroll
+            for (int g = 0; g < QW / 32; ++g) tmem_ld32(t_lane + COL_S + col0 + 32 * g, *reinterpret_cast<uint32_t(*)[32]>(&p[32 * g]));
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(sh.bar.s_free));
 
-            const bool clear = !padded && c0 >= lo && c0 + KQW <= hi;
+            const bool clear = !padded && c0 >= lo && c0 + QW <= hi;
             if (!__all_sync(0xffffffffu, clear)) {
 #pragma unroll
-                for (int c = 0; c < KQW; ++c) {
+                for (int c = 0; c < QW; ++c) {
                     const int key = c0 + c;
-                    p[c] = (key >= lo && key < hi && !((pb >> c) & 1u)) ? p[c] : -INFINITY;
+                    p[c] = (key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u)) ? p[c] : -INFINITY;
                 }
             }
 #pragma unroll
-            for (int c4 = 0; c4 < KQW / 4; ++c4) {
-                p[c4 * 4 + 0] = exp2_mixed<(poly_of4_dq<T>() > 3)>(fmaf(p[c4 * 4 + 0], a.scale_log2, -l2));
-                p[c4 * 4 + 1] = exp2_mixed<(poly_of4_dq<T>() > 1)>(fmaf(p[c4 * 4 + 1], a.scale_log2, -l2));
-                p[c4 * 4 + 2] = exp2_mixed<(poly_of4_dq<T>() > 2)>(fmaf(p[c4 * 4 + 2], a.scale_log2, -l2));
-                p[c4 * 4 + 3] = exp2_mixed<(poly_of4_dq<T>() > 0)>(fmaf(p[c4 * 4 + 3], a.scale_log2, -l2));
-            }
+            for (int c = 0; c < QW; ++c) p[c] = ex2(fmaf(p[c], a.scale_log2, -l2));
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full[st]), (t >> 1) & 1))) { failed = true; break; }
             tc_fence_after_sync();
-            {
-                float dp[KQW];
-                tmem_ld32(t_lane + COL_DP + st * BIG + col0, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
-                tmem_ld_wait();
-                uint32_t ds[KQW / 2];
 #pragma unroll
-                for (int c2 = 0; c2 < KQW / 2; ++c2)
-                    ds[c2] = Pack<T>::two(p[2 * c2] * (dp[2 * c2] - dl), p[2 * c2 + 1] * (dp[2 * c2 + 1] - dl));
-                tmem_st16(t_lane + COL_DP + st * BIG + col0, ds);   // over the first half of the f32 columns just read
+            for (int g = 0; g < QW / 32; ++g) {
+                float dp[32];
+                tmem_ld32(t_lane + COL_DP + st * BIG + col0 + 32 * g, *reinterpret_cast<uint32_t(*)[32]>(&dp[0]));
+                tmem_ld_wait();
+                uint32_t ds[16];
+#pragma unroll
+                for (int c2 = 0; c2 < 16; ++c2)
+                    ds[c2] = Pack<T>::two(p[32 * g + 2 * c2] * (dp[2 * c2] - dl), p[32 * g + 2 * c2 + 1] * (dp[2 * c2 + 1] - dl));
+                tmem_st16(t_lane + COL_DP + st * BIG + col0 + 32 * g, ds);   // over the first half of the f32 columns just read
             }
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(sh.bar.ds_full[st]));
         }
-        constexpr int EC = 32;   // columns of the row per thread (HD = 64: the first two of the four warps of a quadrant)
-        const bool mine = cg < HD / EC;
+        // ---------------- epilogue: the row's HD columns over the quadrant's warps, 32 at a time ----------------
+        constexpr int EC = 32;
+        constexpr int PER = (HD / EC + QCG - 1) / QCG;   // 32-column chunks of the row per warp of the quadrant
         if (steps == 0 || failed) {
-            T *dq = static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + cg * EC;
-            if (row < a.tq && !failed && mine) store_zero_cols<T, EC / 8>(dq);
+            if (row < a.tq && !failed) {
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    const int ch = cg * PER + i;
+                    if (ch < HD / EC) store_zero_cols<T, EC / 8>(static_cast<T *>(a.dq) + (((int64_t)b * a.tq + row) * a.hq + h) * HD + ch * EC);
+                }
+            }
         } else if (__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.acc_ready), 0))) {
             // Every MMA has completed, so the resident Q is dead: the scaled rows of dQ are staged
             // over it in the layout of the TMA box and leave as two bulk stores (whole lines instead
             // of 64 bytes per thread and row; rows past the last query are dropped).
             tc_fence_after_sync();
-            uint32_t o[32];
-            if (mine) tmem_ld32(t_lane + COL_DQ + cg * EC, o);
-            tmem_ld_wait();
-            uint8_t *half_row = q_s + (cg >> 1) * BIG_HALF + r * 128;
 #pragma unroll
-            for (int e = 0; e < 4 && mine; ++e) {
-                uint4 v;
-                v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * a.scale, __uint_as_float(o[8 * e + 1]) * a.scale);
-                v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * a.scale, __uint_as_float(o[8 * e + 3]) * a.scale);
-                v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * a.scale, __uint_as_float(o[8 * e + 5]) * a.scale);
-                v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * a.scale, __uint_as_float(o[8 * e + 7]) * a.scale);
-                const int chunk = (cg & 1) * 4 + e;   // 16-byte chunk of the half row
-                *reinterpret_cast<uint4 *>(half_row + ((chunk ^ (r & 7)) << 4)) = v;
+            for (int i = 0; i < PER; ++i) {
+                const int ch = cg * PER + i;   // 32-column chunk of the row
+                if (ch < HD / EC) {
+                    uint32_t o[32];
+                    tmem_ld32(t_lane + COL_DQ + ch * EC, o);
+                    tmem_ld_wait();
+                    uint8_t *half_row = q_s + (ch >> 1) * BIG_HALF + r * 128;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 v;
+                        v.x = Pack<T>::two(__uint_as_float(o[8 * e + 0]) * a.scale, __uint_as_float(o[8 * e + 1]) * a.scale);
+                        v.y = Pack<T>::two(__uint_as_float(o[8 * e + 2]) * a.scale, __uint_as_float(o[8 * e + 3]) * a.scale);
+                        v.z = Pack<T>::two(__uint_as_float(o[8 * e + 4]) * a.scale, __uint_as_float(o[8 * e + 5]) * a.scale);
+                        v.w = Pack<T>::two(__uint_as_float(o[8 * e + 6]) * a.scale, __uint_as_float(o[8 * e + 7]) * a.scale);
+                        const int chunk = (ch & 1) * 4 + e;   // 16-byte chunk of the half row
+                        *reinterpret_cast<uint4 *>(half_row + ((chunk ^ (r & 7)) << 4)) = v;
+                    }
+                }
             }
             tc_fence_before_sync();
         } else {
@@ -962,7 +980,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             // that gave up marks the tile, and nothing is stored from a tile that is not whole.
             if (failed && lane == 0) sh.tile_bad = 1;
             fence_proxy_async_smem();
-            named_barrier(1, KEW_THREADS);
+            named_barrier(1, QEW_THREADS);
             if (sw == 0 && lane == 0 && sh.tile_bad == 0) {
                 tma_store_4d(&tm_dq, smem_u32(q_s), 0, h, m0, b);
                 if constexpr (HD > 64) tma_store_4d(&tm_dq, smem_u32(q_s + BIG_HALF), 64, h, m0, b);
