@@ -280,11 +280,13 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             auto sub_step = [&](auto r_, int i, int u) -> bool {
                 constexpr int R = decltype(r_)::value, st = R >> 1, half = R & 1;
                 const bool more = u + 2 < subs;
+                // (One vote over all the waits of the run: the lanes leave together, whatever a wait answers.)
+                bool ok = mbar_wait(FWD2_BAR(p_full) + 8 * (2 * t + half), st);
                 if (half == 0) {
-                    if (!mbar_wait(FWD2_BAR(v_full) + 8 * st, i & 1)) return false;
-                    if (more && !mbar_wait(FWD2_BAR(k_full) + 8 * (st ^ 1), (i + st) & 1)) return false;
+                    ok = mbar_wait(FWD2_BAR(v_full) + 8 * st, i & 1) && ok;
+                    if (more) ok = mbar_wait(FWD2_BAR(k_full) + 8 * (st ^ 1), (i + st) & 1) && ok;
                 }
-                if (!mbar_wait(FWD2_BAR(p_full) + 8 * (2 * t + half), st)) return false;
+                if (!__all_sync(0xffffffffu, ok)) return false;
                 tc_fence_after_sync();
                 if (elect_one()) {
 #pragma unroll
@@ -306,7 +308,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 return true;
             };
             // Two sub-steps of S ahead ...
-            if (!(mbar_wait(FWD2_BAR(q_full), 0) && mbar_wait(FWD2_BAR(k_full), 0))) failed = true;
+            if (!__all_sync(0xffffffffu, mbar_wait(FWD2_BAR(q_full), 0) && mbar_wait(FWD2_BAR(k_full), 0))) failed = true;
             if (!failed) {
                 tc_fence_after_sync();
                 if (elect_one()) {
