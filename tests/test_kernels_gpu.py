@@ -126,6 +126,29 @@ def test_the_lazy_maximum_moves_again_and_again(adapter, case, dtype):
     R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), bounds)
 
 
+def many_sequences(n, seed):
+    lengths = [int(x) for x in (oracle.seeded((n,), seed) * 40 + 90).clip(1, 170)]
+    lengths[3] = 0
+    t = sum(lengths)
+    mask = AttentionMask.packed(K.offsets(lengths), K.offsets(lengths))
+    return K.seeded(f"{n} packed sequences", [1, 4, 2, t, t, 128], mask, AttentionOptions.causal_(), seed)
+
+
+MANY = [many_sequences(31, 401), many_sequences(32, 402), many_sequences(57, 403)]
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("case", MANY, ids=[c.name for c in MANY])
+def test_rows_are_placed_in_many_packed_sequences(adapter, case, dtype):
+    """A warp of the forward and of dq places its 32 rows in the packed batch with one offset per lane
+    when the batch has at most 31 sequences, and by bisection per thread beyond: both sides of that
+    line, an empty sequence among them."""
+    before = _lib.probe("tensor_core_runs")
+    got = run_case(adapter, case, dtype)
+    assert _lib.probe("tensor_core_runs") == before + 2
+    R.check(f"{dtype.name} {case.name}", [got.out, got.lse, *got.grads], oracle_results(case), OWN[dtype])
+
+
 TC64_CASES = K.tensor_core_cases(64)
 
 
