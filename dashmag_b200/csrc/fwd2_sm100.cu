@@ -370,17 +370,43 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             // Row maximum: eight independent chains of three-input maxima, then a tree.
-            auto row_max = [&]() {
-                float mx8[8];
+            float mx8[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) mx8[e] = fmax3(s[e], s[8 + e], s[16 + e]);
+            for (int e = 0; e < 8; ++e) mx8[e] = fmax3(s[e], s[8 + e], s[16 + e]);
 #pragma unroll
-                for (int c = 24; c < SN; c += 16)
+            for (int c = 24; c < SN; c += 16)
 #pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        mx8[e] = c + 8 + e < SN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
-                return fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
-            };
+                for (int e = 0; e < 8; ++e)
+                    mx8[e] = c + 8 + e < SN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
+            const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+            // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8 - or by
+            // anything at all, for a row of few keys (see EXACT_KEYS).
+            float factor = 1.f;
+            bool rescale = false;
+            if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated yet for this row (or exact zeros)
+            } else if ((mx - m_ref) * a.scale_log2 > rescale_at) {
+                // The difference of the two offsets as the exponentials use them (each product rounded on its
+                // own), so that what was summed before and what is summed from here on share one reference.
+                factor = ex2(__fsub_rn(__fmul_rn(m_ref, a.scale_log2), __fmul_rn(mx, a.scale_log2)));
+                l *= factor;
+                m_ref = mx;
+                rescale = true;
+            }
+            const float neg = m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
+            const float2 neg2 = make_float2(neg, neg);
+
+            // Only a moved reference touches O, and it has to see sub-steps 0..u-1 in it.  P V of u - 2 has
+            // completed (S of this sub-step was issued behind it); P V of u - 1 - whose P this warp arrived a
+            // moment ago - may not have.  S of u + 1 is issued behind it, so the warp waits for that (the
+            // barrier it waits on at the next sub-step anyway: of its phases, that of S(u - 1) has completed
+            // and that of S(u + 3) cannot have), or for o_tail at the last sub-step.
+            if (u > 0 && __any_sync(0xffffffffu, rescale)) {
+                const bool ok = u + 1 < subs ? mbar_wait(BAR(sh.bar.s_full[t][buf ^ 1]), ((u + 1) >> 1) & 1)
+                                             : mbar_wait(BAR(sh.bar.o_tail[t]), 0);
+                if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
+                rescale_accumulator<HD>(t_lane + COL_O(t), factor);
+            }
             // The special-function pipe takes one warp instruction in eight cycles: the 64 exponentials of a
             // warp are 512 cycles of it, and the two softmax warps of a scheduler - one per tile - that run
             // them at the same time each take twice that, after which the pipe stands idle while both do the
@@ -388,96 +414,33 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // u, then tile 1's, then tile 0's of u + 1 ..., each doing the rest of its sub-step (the wait for
             // S, the maximum, the store of P) under the other's turn.  (Bounded waits on barriers of the
             // block's own, like every other wait here; both tiles sweep the same sub-steps.)
-            auto my_turn = [&]() {
-                return !(t == 1 || u > 0) || __all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.turn[warp & 3][t]), (t == 1 ? u : u - 1) & 1));
-            };
-            // P = 2^(s scale - reference) over the first 32 columns of the buffer this thread has read (two
-            // 16-bit values a column); returns the row's sum of the sub-step.  `hand_over`: the other tile's
-            // turn begins once the last exponential has been issued - not behind the packing and the store of
-            // P, which need no special-function pipe (the exponentials are volatile asm so that the compiler
-            // keeps them in front of the arrival).
-            auto exponentials = [&](float neg, auto hand_over) {
-                const float2 neg2 = make_float2(neg, neg);
-                float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-                for (int cc = 0; cc < SN / 32; ++cc) {
-                    float pe[32];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
-                        pe[2 * e] = ex2_ordered(x.x);
-                        pe[2 * e + 1] = ex2_ordered(x.y);
-                    }
-                    if (decltype(hand_over)::value && cc == SN / 32 - 1) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(BAR(sh.bar.turn[warp & 3][t ^ 1]));
-                    }
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        sum2[e & 3] = add2(sum2[e & 3], make_float2(pe[2 * e], pe[2 * e + 1]));
-                        pk[e] = Pack<T>::two(pe[2 * e], pe[2 * e + 1]);
-                    }
-                    tmem_st16(t_lane + COL_S(t, buf) + cc * 16, pk);
-                }
-                const float2 tsum = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
-                return tsum.x + tsum.y;
-            };
-            // Rows under the lazy maximum whose reference stands - every row of a long sweep from its second
-            // sub-step on - do not wait for their maximum: the exponentials are taken against the standing
-            // reference at once, the maximum is found beside them (it needs no special-function pipe), and only
-            // if some row of the warp outgrew its reference by 2^8 after all (rare) is the sub-step done again
-            // the long way.  The results are the same bit for bit: an unmoved reference is what the long way
-            // would have used.
-            const bool settled = u > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY && rescale_at != 0.f);
-            float mx = 0.f, psum = 0.f;
-            bool done = false;
-            if (settled) {
-                if (!my_turn()) { failed = true; break; }
-                psum = exponentials(-__fmul_rn(m_ref, a.scale_log2), std::true_type{});
-                mx = row_max();
-                done = !__any_sync(0xffffffffu, (mx - m_ref) * a.scale_log2 > rescale_at);
+            if (t == 1 || u > 0) {
+                if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.turn[warp & 3][t]), (t == 1 ? u : u - 1) & 1))) { failed = true; break; }
             }
-            if (!done) {
-                if (!settled) mx = row_max();
-                // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8 - or by
-                // anything at all, for a row of few keys (see EXACT_KEYS).
-                float factor = 1.f;
-                bool rescale = false;
-                if (m_ref == -INFINITY) {
-                    m_ref = mx;  // nothing accumulated yet for this row (or exact zeros)
-                } else if ((mx - m_ref) * a.scale_log2 > rescale_at) {
-                    // The difference of the two offsets as the exponentials use them (each product rounded on its
-                    // own), so that what was summed before and what is summed from here on share one reference.
-                    factor = ex2(__fsub_rn(__fmul_rn(m_ref, a.scale_log2), __fmul_rn(mx, a.scale_log2)));
-                    l *= factor;
-                    m_ref = mx;
-                    rescale = true;
+            // P over the first 32 columns of the buffer this thread has read (two 16-bit values a column).
+            float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int cc = 0; cc < SN / 32; ++cc) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float2 x = fma2(make_float2(s[cc * 32 + 2 * e], s[cc * 32 + 2 * e + 1]), sl2, neg2);
+                    const float p0 = ex2(x.x), p1 = ex2(x.y);
+                    sum2[e & 3] = add2(sum2[e & 3], make_float2(p0, p1));
+                    pk[e] = Pack<T>::two(p0, p1);
                 }
-                const float neg = m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
-                // Only a moved reference touches O, and it has to see sub-steps 0..u-1 in it.  P V of u - 2 has
-                // completed (S of this sub-step was issued behind it); P V of u - 1 - whose P this warp arrived a
-                // moment ago - may not have.  S of u + 1 is issued behind it, so the warp waits for that (the
-                // barrier it waits on at the next sub-step anyway: of its phases, that of S(u - 1) has completed
-                // and that of S(u + 3) cannot have), or for o_tail at the last sub-step.
-                if (u > 0 && __any_sync(0xffffffffu, rescale)) {
-                    const bool ok = u + 1 < subs ? mbar_wait(BAR(sh.bar.s_full[t][buf ^ 1]), ((u + 1) >> 1) & 1)
-                                                 : mbar_wait(BAR(sh.bar.o_tail[t]), 0);
-                    if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
-                    rescale_accumulator<HD>(t_lane + COL_O(t), factor);
-                }
-                if (settled) {
-                    psum = exponentials(neg, std::false_type{});   // the turn has been taken and handed over already
-                } else {
-                    if (!my_turn()) { failed = true; break; }
-                    psum = exponentials(neg, std::true_type{});
-                }
+                tmem_st16(t_lane + COL_S(t, buf) + cc * 16, pk);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR(sh.bar.turn[warp & 3][t ^ 1]));   // the other tile's turn
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR(sh.bar.p_full[t][buf]));
-            l += psum;
+            {
+                const float2 tsum = add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3]));
+                l += tsum.x + tsum.y;
+            }
         }
         // ---------------- epilogue ----------------
         T *out = static_cast<T *>(a.out);

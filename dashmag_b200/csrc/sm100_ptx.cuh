@@ -297,14 +297,6 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// The same, but kept in program order among the other volatile instructions (barrier arrivals, tensor-memory
-// stores): for code that hands the special-function pipe over right behind its last exponential.
-__device__ __forceinline__ float ex2_ordered(float x) {
-    float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 // 2^x for x <= 0 without the special-function pipe (ten issue slots of the FMA / ALU pipes against
 // one of the MUFU pipe, which takes a warp instruction every eight cycles): round to the nearest
 // integer by the magic-number add, a cubic
