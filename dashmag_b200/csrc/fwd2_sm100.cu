@@ -361,7 +361,12 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_ld_wait();
 
             const bool clear = !padded && k0 >= lo && k0 + SN <= hi;  // the row sees the whole sub-step
-            if (!__all_sync(0xffffffffu, clear)) {
+            // ... or nothing of it: a row of another sequence of the packed batch (a tile that straddles two
+            // sequences sweeps the first one's keys for the second one's rows too), or one whose interval ends
+            // before the sub-step.  Such a row needs no look at its scores: its maximum is -inf and its
+            // exponentials are taken against -inf, which makes them exact zeros.
+            const bool none = !padded && (hi <= k0 || lo >= k0 + SN || hi <= lo);
+            if (!__all_sync(0xffffffffu, clear || none)) {
 #pragma unroll
                 for (int c = 0; c < SN; ++c) {
                     const int key = k0 + c;
@@ -378,7 +383,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
                     mx8[e] = c + 8 + e < SN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
-            const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+            const float mx = none ? -INFINITY : fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
             // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8 - or by
             // anything at all, for a row of few keys (see EXACT_KEYS).
             float factor = 1.f;
@@ -393,7 +398,7 @@ fwd2_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 m_ref = mx;
                 rescale = true;
             }
-            const float neg = m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
+            const float neg = none ? -INFINITY : m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
             const float2 neg2 = make_float2(neg, neg);
 
             // Only a moved reference touches O, and it has to see sub-steps 0..u-1 in it.  P V of u - 2 has
