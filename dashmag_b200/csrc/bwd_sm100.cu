@@ -575,12 +575,23 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             tmem_ld32(t_lane + COL_ST + col0, *reinterpret_cast<uint32_t(*)[32]>(&p[0]));
             tmem_ld_wait();
             const QAux &aux = sh.aux[st];
-            if (!__all_sync(0xffffffffu, c0 >= qa && c0 + KQW <= qb)) {
-                // Some key of the warp is not seen by all of these queries: hide what it is not
-                // seen by before the exponentials, in a pass of its own so that the common,
-                // unmasked step pays nothing for it.
+            const bool all_of_them = c0 >= qa && c0 + KQW <= qb;
+            if (!__all_sync(0xffffffffu, all_of_them)) {
+                // Some key of the warp is not seen by all of these queries: hide what it is not seen by
+                // before the exponentials, in a pass of its own so that the common, unmasked step pays
+                // nothing for it.  A key that is seen by NONE of them - a key of another sequence of the
+                // packed batch, in a block of keys that straddles two - needs no comparisons: where every key
+                // of the warp is seen by all or by none, those rows are simply set.
+                const bool none_of_them = c0 + KQW <= qa || c0 >= qb || qb <= qa;
+                if (__all_sync(0xffffffffu, all_of_them || none_of_them)) {
+                    if (none_of_them) {
 #pragma unroll
-                for (int c = 0; c < KQW; ++c) p[c] = (c0 + c >= qa && c0 + c < qb) ? p[c] : -INFINITY;
+                        for (int c = 0; c < KQW; ++c) p[c] = -INFINITY;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < KQW; ++c) p[c] = (c0 + c >= qa && c0 + c < qb) ? p[c] : -INFINITY;
+                }
             }
             // P^T over the first half of the f32 columns this thread has just read, in two halves of
             // 16 queries (8 columns): the tensor cores start on the first while the second is made.
@@ -908,15 +919,20 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             if (lane == 0) mbar_arrive(BAR(sh.bar.s_free));
 
             const bool clear = !padded && c0 >= lo && c0 + QW <= hi;
-            if (!__all_sync(0xffffffffu, clear)) {
+            // ... or sees none of them: a row of another sequence of the packed batch (a tile that straddles two
+            // sequences sweeps the first one's keys for the second one's rows too), or one whose interval ends
+            // before these keys.  Such a row needs no masking pass: against +inf its exponentials are exact zeros.
+            const bool none = !padded && (hi <= c0 || lo >= c0 + QW || hi <= lo);
+            if (!__all_sync(0xffffffffu, clear || none)) {
 #pragma unroll
                 for (int c = 0; c < QW; ++c) {
                     const int key = c0 + c;
                     p[c] = (key >= lo && key < hi && !((pb[c >> 5] >> (c & 31)) & 1u)) ? p[c] : -INFINITY;
                 }
             }
+            const float off = none ? INFINITY : l2;
 #pragma unroll
-            for (int c = 0; c < QW; ++c) p[c] = ex2(fmaf(p[c], a.scale_log2, -l2));
+            for (int c = 0; c < QW; ++c) p[c] = ex2(fmaf(p[c], a.scale_log2, -off));
             if (!__all_sync(0xffffffffu, mbar_wait(BAR(sh.bar.dp_full[st]), (t >> 1) & 1))) { failed = true; break; }
             tc_fence_after_sync();
 #pragma unroll
