@@ -363,9 +363,20 @@ __device__ __forceinline__ void bwd256_pass(const CUtensorMap *r1, const CUtenso
             }
             const bool clear = !padded && c0 >= lo && c0 + CW <= hi;
             if (!__all_sync(0xffffffffu, clear)) {
+                // A row that sees none of these columns (it belongs to another sequence of the packed batch, or
+                // its interval ends before them) needs no comparisons: where every row of the warp sees all or
+                // none, those rows are simply set.
+                const bool none = !padded && (hi <= c0 || lo >= c0 + CW || hi <= lo);
+                if (__all_sync(0xffffffffu, clear || none)) {
+                    if (none) {
 #pragma unroll
-                for (int c = 0; c < CW; ++c)
-                    p[c] = (c0 + c >= lo && c0 + c < hi && !((pb >> c) & 1u)) ? p[c] : -INFINITY;
+                        for (int c = 0; c < CW; ++c) p[c] = -INFINITY;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < CW; ++c)
+                        p[c] = (c0 + c >= lo && c0 + c < hi && !((pb >> c) & 1u)) ? p[c] : -INFINITY;
+                }
             }
             const ColumnAux &aux = sh.aux[st];
 #pragma unroll

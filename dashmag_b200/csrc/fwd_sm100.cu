@@ -271,7 +271,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             tmem_ld_wait();
 
             const bool clear = !padded && k0 >= lo && k0 + BN <= hi;  // the row sees the whole tile
-            if (!__all_sync(0xffffffffu, clear)) {
+            // ... or nothing of it (a row of another sequence of the packed batch, or one whose interval ends
+            // before the tile): no look at its scores is needed, its maximum is -inf and its exponentials are
+            // taken against -inf, which makes them exact zeros.
+            const bool none = !padded && (hi <= k0 || lo >= k0 + BN || hi <= lo);
+            if (!__all_sync(0xffffffffu, clear || none)) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int key = k0 + c;
@@ -288,7 +292,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
                     mx8[e] = c + 8 + e < BN ? fmax3(mx8[e], s[c + e], s[c + 8 + e]) : fmaxf(mx8[e], s[c + e]);
-            const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+            const float mx = none ? -INFINITY : fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
             // Lazy maximum: move the reference only when the row's maximum outgrew it by 2^8 - or by
             // anything at all, for a row of few keys (see EXACT_KEYS).
             float factor = 1.f;
@@ -303,7 +307,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 m_ref = mx;
                 rescale = true;
             }
-            const float neg = m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
+            const float neg = none ? -INFINITY : m_ref == -INFINITY ? 0.f : -__fmul_rn(m_ref, a.scale_log2);
 
             uint32_t pk[BN / 2];  // P of this row, two keys per 32-bit column
             const float2 sl2 = make_float2(a.scale_log2, a.scale_log2), neg2 = make_float2(neg, neg);
